@@ -1,0 +1,30 @@
+"""Shared pytest set-up: the `gpu` marker, import paths, IEEE float32 matrix products."""
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+for extra in (ROOT, ROOT / "tests"):
+    if str(extra) not in sys.path:
+        sys.path.insert(0, str(extra))
+
+# A float32 oracle must be float32: TF32 has half precision's mantissa.
+torch.backends.cuda.matmul.allow_tf32 = False
+torch.backends.cudnn.allow_tf32 = False
+torch.set_float32_matmul_precision("highest")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
