@@ -1,0 +1,188 @@
+"""One step's batch, flattened: the tokens of all entries in a row, and beside them
+everything a kernel needs to know where a token stands.
+
+The reference pads a step to a rectangle [rows, longest] with a boolean mask and
+rebuilds slot index tensors row by row (engine/model.py:435-446,
+engine/attention.py:556-586). Here nothing is padded: an entry is (request, its next
+tokens, the places whose logits are wanted); tokens of all entries are laid end to end,
+and the causal rule j <= position is evaluated inside the attention kernel from
+`q_pos0` and `kv_len`. All integer arrays of a step travel to the device in one copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+
+
+@dataclass(frozen=True)
+class StepEntry:
+    """One request's share of a step: its next tokens (a portion of its prompt, or one
+    decoded token) and the offsets among them whose logits are wanted."""
+
+    key: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class GroupStep:
+    """Per page group: the block tables of the step's entries and every token's slot."""
+
+    block_table: torch.Tensor     # int32 [entries, pages]
+    slots: torch.Tensor           # int32 [tokens]: page id * page_size + offset
+
+
+@dataclass
+class StepContext:
+    ops: Any
+    dtype: torch.dtype
+    device: torch.device
+    num_tokens: int
+    num_seqs: int
+    token_ids: torch.Tensor       # int32 [tokens]
+    positions: torch.Tensor       # int32 [tokens]
+    seq_index: torch.Tensor       # int32 [tokens]: which entry a token belongs to
+    q_start: torch.Tensor         # int32 [entries + 1]: first token of each entry
+    q_pos0: torch.Tensor          # int32 [entries]: position of an entry's first token
+    kv_len: torch.Tensor          # int32 [entries]: tokens of the request after this step
+    state_slot: torch.Tensor      # int32 [entries]
+    logit_rows: torch.Tensor      # int32 [wanted]: token rows whose logits are wanted
+    max_q_len: int
+    max_kv_len: int
+    groups: list[GroupStep]
+    # Host copies, for parts (and tests) that plan on the host.
+    host_q_lens: list[int] = field(default_factory=list)
+    host_q_pos0: list[int] = field(default_factory=list)
+    host_state_slots: list[int] = field(default_factory=list)
+    memo: dict = field(default_factory=dict)
+
+
+class _Staging:
+    """Pinned host buffers that take turns, so that a buffer is not refilled while the
+    copy out of it may still be in flight."""
+
+    def __init__(self, device: torch.device, turns: int = 4) -> None:
+        self.device = device
+        self.pinned = device.type == "cuda"
+        self.buffers: list[torch.Tensor | None] = [None] * turns
+        self.events: list[Any] = [None] * turns
+        self.turn = 0
+
+    def upload(self, flat: np.ndarray) -> torch.Tensor:
+        if not self.pinned:
+            return torch.from_numpy(flat.copy())
+        i = self.turn
+        self.turn = (self.turn + 1) % len(self.buffers)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.buffers[i]
+        if buf is None or buf.numel() < flat.size:
+            buf = torch.empty(max(flat.size, 4096), dtype=torch.int32).pin_memory()
+            self.buffers[i] = buf
+        buf[: flat.size].copy_(torch.from_numpy(flat))
+        out = torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        out.copy_(buf[: flat.size], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self.events[i] = event
+        return out
+
+
+def _pack(sections: list[np.ndarray]) -> tuple[np.ndarray, list[tuple[int, int]]]:
+    """Concatenates int32 arrays, each starting on a 16-byte boundary."""
+    spans = []
+    total = 0
+    for s in sections:
+        spans.append((total, s.size))
+        total += (s.size + 3) // 4 * 4
+    flat = np.zeros(max(total, 4), dtype=np.int32)
+    for (start, size), s in zip(spans, sections):
+        flat[start : start + size] = s.reshape(-1)
+    return flat, spans
+
+
+class BatchBuilder:
+    def __init__(self, manager: CacheManager, ops: Any, dtype: torch.dtype, device) -> None:
+        self.manager = manager
+        self.ops = ops
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.staging = _Staging(self.device)
+
+    def build(self, entries: Sequence[StepEntry]) -> StepContext:
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        manager = self.manager
+        page = manager.block_size
+        seen = set()
+        q_lens, pos0, slots_of = [], [], []
+        for e in entries:
+            if e.key in seen:
+                raise ValueError(f"request {e.key!r} appears twice in one step")
+            seen.add(e.key)
+            n = len(e.tokens)
+            if n < 1:
+                raise ValueError(f"request {e.key!r}: an entry needs at least one token")
+            start = manager.num_computed(e.key)
+            if start + n > manager.num_reserved(e.key):
+                raise ValueError(
+                    f"request {e.key!r}: tokens {start}..{start + n - 1} run, "
+                    f"room is reserved for {manager.num_reserved(e.key)}"
+                )
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.key!r}: wanted place {w} is outside its {n} tokens")
+            q_lens.append(n)
+            pos0.append(start)
+            slots_of.append(manager.slot_of(e.key))
+
+        b = len(entries)
+        q_start = np.zeros(b + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        total = int(q_start[-1])
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        seq_index = np.repeat(np.arange(b, dtype=np.int32), q_lens)
+        positions = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
+        kv_len = np.asarray(pos0, dtype=np.int32) + np.asarray(q_lens, dtype=np.int32)
+        rows = [int(q_start[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
+        logit_rows = np.asarray(rows, dtype=np.int32)
+
+        sections = [
+            token_ids, positions, seq_index, q_start, np.asarray(pos0, dtype=np.int32), kv_len,
+            np.asarray(slots_of, dtype=np.int32), logit_rows,
+        ]
+        max_kv = int(kv_len.max())
+        width = (max_kv + page - 1) // page
+        for g in range(len(manager.groups)):
+            table = manager.table_rows(g, slots_of, width)
+            page_of_token = table[seq_index, positions // page]
+            if (page_of_token < 0).any():
+                bad = int(np.argmax(page_of_token < 0))
+                raise ValueError(
+                    f"request {entries[int(seq_index[bad])].key!r}: position {int(positions[bad])} has no page in group {g}"
+                )
+            sections += [np.ascontiguousarray(table), page_of_token * page + positions % page]
+
+        flat, spans = _pack(sections)
+        dev = self.staging.upload(flat)
+
+        def part(i: int) -> torch.Tensor:
+            start, size = spans[i]
+            return dev[start : start + size]
+
+        groups = []
+        for g in range(len(manager.groups)):
+            groups.append(GroupStep(part(8 + 2 * g).view(b, width), part(9 + 2 * g)))
+        return StepContext(
+            ops=self.ops, dtype=self.dtype, device=self.device, num_tokens=total, num_seqs=b,
+            token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
+            kv_len=part(5), state_slot=part(6), logit_rows=part(7),
+            max_q_len=max(q_lens), max_kv_len=max_kv, groups=groups,
+            host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
+        )

@@ -1,0 +1,63 @@
+"""The decoder that runs: parts built from a `ModelSpec`, run in the schedule's order.
+
+The reference writes its model once as a Python loop over identical layers
+(engine/model.py:322-351). Here the loop runs over the schedule; each entry names a
+layer (whose parts may differ from every other layer's) and the cache it reads and
+writes. One call of `forward` is one traversal, counted in `forward_pass_count`
+as the reference counts it (engine/model.py:180-186,338) so that a test can tell a
+batched step from a loop over requests.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from ..config.model_spec import ModelSpec
+from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Runtime
+
+
+@dataclass
+class Layer:
+    block: Any
+    mixer_norm: Any
+    mixer: Any
+    feed_forward_norm: Any
+    feed_forward: Any
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        self.spec = spec
+        self.runtime = runtime
+        self.ops = runtime.ops
+        self.embedding = EMBEDDINGS.get(spec.embedding.kind)(spec.embedding, tensors, runtime)
+        self.head = HEADS.get(spec.head.kind)(spec.head, tensors, runtime)
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, tensors, runtime)
+        self.layers: list[Layer] = []
+        for layer in spec.layers:
+            self.layers.append(
+                Layer(
+                    block=BLOCKS.get(layer.block)(),
+                    mixer_norm=NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, tensors, runtime),
+                    mixer=MIXERS.get(layer.mixer.kind)(layer.mixer, tensors, runtime),
+                    feed_forward_norm=NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, runtime),
+                    feed_forward=FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, tensors, runtime),
+                )
+            )
+        self.forward_pass_count = 0
+
+    def forward(self, ctx, entry_caches) -> torch.Tensor | None:
+        """Runs the step's tokens through every schedule entry; float32 logits
+        [wanted, vocab] at `ctx.logit_rows`, or None when nothing is wanted."""
+        self.forward_pass_count += 1
+        hidden = self.embedding.forward(ctx)
+        for position, entry in enumerate(self.spec.schedule):
+            layer = self.layers[entry.layer]
+            hidden = layer.block.forward(ctx, hidden, layer, entry_caches[position])
+        if ctx.logit_rows.numel() == 0:
+            return None
+        rows = self.ops.gather_rows(hidden, ctx.logit_rows)
+        return self.head.forward(ctx, self.final_norm.forward(ctx, rows))
