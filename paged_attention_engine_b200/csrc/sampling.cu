@@ -1,0 +1,109 @@
+// Sampling on the device from float32 logits: greedy, and temperature by the Gumbel-max
+// rule. The reference samples greedily on the host, one argmax and one device-to-host
+// read per row (engine/scheduler.py:610); temperature sampling has no counterpart there.
+//
+// Row r takes token argmax_j (logits[r, j] / T_r + g_j) with g_j = -log(-log(u_j)) and
+// u_j a uniform number in (0, 1) that is a pure function of (seed, request key, index of
+// the output token, j): a counter-based generator, so the draw does not depend on what
+// else is in the batch, on how the prompt was cut, or on a preemption in between.
+// T_r == 0 is plain argmax; ties go to the lowest index.
+#include "common.cuh"
+
+#include <cfloat>
+
+using namespace pae;
+
+namespace {
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x85EBCA6Bu;
+  x ^= x >> 13;
+  x *= 0xC2B2AE35u;
+  x ^= x >> 16;
+  return x;
+}
+
+__device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
+  return v > best || (v == best && i < best_i);
+}
+
+constexpr int THREADS = 512;
+
+__global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
+                                                         const float* __restrict__ temperature,
+                                                         const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
+                                                         const int* __restrict__ request_key,
+                                                         const int* __restrict__ output_index, int vocab) {
+  __shared__ float best_v[THREADS / 32];
+  __shared__ int best_i[THREADS / 32];
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  const float t = temperature[r];
+  uint32_t h = 0;
+  if (t > 0.f) {
+    h = mix32((uint32_t)seed_lo[r] ^ 0x9E3779B9u);
+    h = mix32(h ^ (uint32_t)seed_hi[r]);
+    h = mix32(h + (uint32_t)request_key[r] * 0x7FEB352Du);
+    h = mix32(h + (uint32_t)output_index[r] * 0x846CA68Bu);
+  }
+  const float inv_t = t > 0.f ? 1.f / t : 1.f;
+  float v_best = -FLT_MAX;
+  int i_best = 0x7fffffff;
+  for (int j = threadIdx.x; j < vocab; j += THREADS) {
+    float v = row[j];
+    if (t > 0.f) {
+      const uint32_t hv = mix32(h + (uint32_t)j * 0x9E3779B1u);
+      const float u = ((float)(hv >> 9) + 0.5f) * (1.0f / 8388608.0f);
+      v = v * inv_t - logf(-logf(u));
+    }
+    if (better(v, j, v_best, i_best)) {
+      v_best = v;
+      i_best = j;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
+    if (better(ov, oi, v_best, i_best)) {
+      v_best = ov;
+      i_best = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    best_v[warp] = v_best;
+    best_i[warp] = i_best;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    v_best = lane < THREADS / 32 ? best_v[lane] : -FLT_MAX;
+    i_best = lane < THREADS / 32 ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
+      if (better(ov, oi, v_best, i_best)) {
+        v_best = ov;
+        i_best = oi;
+      }
+    }
+    if (lane == 0) tokens[r] = i_best == 0x7fffffff ? 0 : i_best;
+  }
+}
+
+}  // namespace
+
+// tokens int32 [rows]; logits float32 [rows, vocab]; per row: temperature (float32),
+// the two halves of the 64-bit seed, the request's key and the index of the output token.
+PAE_EXPORT int pae_sample(int* tokens, const float* logits, const float* temperature, const int* seed_lo,
+                          const int* seed_hi, const int* request_key, const int* output_index, int rows, int vocab,
+                          void* stream) {
+  if (rows == 0) return 0;
+  if (vocab < 1) return fail(2, "sample: vocabulary of %d", vocab);
+  sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(tokens, logits, temperature, seed_lo, seed_hi, request_key, output_index, vocab);
+  return check_launch("sample");
+}
+
+PAE_DEFINE_LAST_ERROR()

@@ -1,0 +1,111 @@
+"""From a model folder to something that steps: configuration, weights, parts, cache.
+
+`Engine` owns the model (parts built from the folder's config.json through the
+architecture registry, tensors read from its safetensors) and hands out paged caches
+and runners for it, in the manner of the reference's `Qwen2Engine.from_hf_model` /
+`new_paged_cache` (engine/model.py:190-229,257-272), but from files, for any registered
+architecture, and with no code path that runs without the CUDA kernels.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Any, Mapping
+
+import torch
+
+from ..cache import CacheManager, PagedKVCache, plan_cache
+from ..config import ModelSpec, resolve, resolve_folder
+from ..parts import Runtime
+from ..weights import load_tensors, place_tensors, random_tensors
+from .model import DecoderModel
+from .runner import ModelRunner
+
+DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "fp32": torch.float32, "f32": torch.float32,
+}
+
+
+def as_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"dtype {dtype} is not supported (bfloat16 or float32)")
+        return dtype
+    try:
+        return DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype '{dtype}' is not supported (bfloat16 or float32)") from None
+
+
+def _default_ops():
+    from ..kernels import ops
+
+    ops.require_cuda()
+    return ops
+
+
+class Engine:
+    def __init__(self, config: Any, spec: ModelSpec, tensors: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        self.config = config
+        self.spec = spec
+        self.runtime = runtime
+        self.dtype = runtime.dtype
+        self.device = runtime.device
+        self.cache_plan = plan_cache(spec)
+        self.model = DecoderModel(spec, tensors, runtime)
+
+    # -- construction ------------------------------------------------------ #
+
+    @classmethod
+    def from_pretrained(cls, folder: str | Path, dtype="bfloat16", device="cuda:0", ops=None) -> "Engine":
+        """Reads config.json and the safetensors of `folder`; the architecture named in
+        config.json chooses the model."""
+        dtype = as_dtype(dtype)
+        config, spec = resolve_folder(folder)
+        runtime = Runtime(ops or _default_ops(), dtype, torch.device(device))
+        tensors = load_tensors(folder, spec, dtype, runtime.device)
+        return cls(config, spec, tensors, runtime)
+
+    @classmethod
+    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0", ops=None) -> "Engine":
+        """Random weights drawn on the device, without a folder (for measurements of large shapes)."""
+        dtype = as_dtype(dtype)
+        config, spec = resolve(raw_config)
+        runtime = Runtime(ops or _default_ops(), dtype, torch.device(device))
+        tensors = random_tensors(raw_config, seed, dtype, runtime.device)
+        tensors = place_tensors(tensors, spec, dtype, runtime.device, "random weights")
+        return cls(config, spec, tensors, runtime)
+
+    # -- caches and runners ------------------------------------------------ #
+
+    def new_paged_cache(self, num_blocks: int, block_size: int = 16, max_num_seqs: int = 256) -> PagedKVCache:
+        """A pool of `num_blocks` pages of `block_size` tokens for every page group of the model."""
+        manager = CacheManager(self.cache_plan.groups, num_blocks, block_size, max_num_seqs)
+        return PagedKVCache(self.cache_plan, manager, self.dtype, self.device)
+
+    def new_runner(self, cache: PagedKVCache) -> ModelRunner:
+        return ModelRunner(self.model, cache)
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    def weight_bytes(self) -> int:
+        """Bytes of every distinct weight tensor that a step reads."""
+        seen: dict[int, int] = {}
+
+        def visit(obj: Any) -> None:
+            for value in vars(obj).values():
+                if isinstance(value, torch.Tensor):
+                    seen[value.data_ptr()] = value.numel() * value.element_size()
+                elif hasattr(value, "runtime") and value is not obj:
+                    visit(value)
+
+        model = self.model
+        for part in (model.embedding, model.head, model.final_norm):
+            visit(part)
+        for layer in model.layers:
+            for part in (layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward):
+                visit(part)
+        return sum(seen.values())

@@ -1,0 +1,137 @@
+"""Builds the CUDA libraries of `csrc/` for sm_100a with nvcc, on first use.
+
+Each kernel family is one `.cu` file and becomes one shared library that `ops.py`
+loads with ctypes (the entry points are `extern "C"` and take raw pointers, so no
+Python or torch headers are compiled). A library's file name carries a hash of its
+sources and flags; it is built when no file of that name exists, in the package's own
+`_build/` folder, or under the system's temporary folder when the package cannot be
+written to. Only the families that a model asks for are built. Progress lines go to
+stderr while nvcc runs.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent.parent / "csrc"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC", "-shared",
+]
+
+# family -> sources (the first is compiled, the others are headers it includes)
+FAMILIES: dict[str, list[str]] = {
+    "elementwise": ["elementwise.cu", "common.cuh"],
+    "gemm_simt": ["gemm_simt.cu", "common.cuh"],
+    "attention_simt": ["attention_simt.cu", "common.cuh"],
+    "sampling": ["sampling.cu", "common.cuh"],
+}
+
+_lock = threading.Lock()
+
+
+def say(message: str) -> None:
+    print(f"[paged_attention_engine_b200] {message}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    for candidate in (
+        os.environ.get("PAE_NVCC"),
+        shutil.which("nvcc"),
+        os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+        "/usr/local/cuda/bin/nvcc",
+    ):
+        if candidate and os.path.isfile(candidate) and os.access(candidate, os.X_OK):
+            return candidate
+    raise RuntimeError(
+        "nvcc was not found (PATH, CUDA_HOME, /usr/local/cuda): the CUDA kernels cannot be built, "
+        "and this engine has no other path"
+    )
+
+
+def build_dir() -> Path:
+    """The package's own `_build/` when it can be written to, else a per-user temporary folder."""
+    own = Path(__file__).resolve().parent.parent / "_build"
+    try:
+        own.mkdir(exist_ok=True)
+        probe = own / f".write_probe_{os.getpid()}"
+        probe.write_text("")
+        probe.unlink()
+        return own
+    except OSError:
+        fallback = Path(tempfile.gettempdir()) / f"paged_attention_engine_b200_build_{os.getuid()}"
+        fallback.mkdir(parents=True, exist_ok=True)
+        return fallback
+
+
+def family_hash(name: str) -> str:
+    digest = hashlib.sha256()
+    for source in FAMILIES[name]:
+        digest.update(source.encode())
+        digest.update((CSRC / source).read_bytes())
+    digest.update(" ".join(NVCC_FLAGS).encode())
+    return digest.hexdigest()[:12]
+
+
+def library_path(name: str, folder: Path | None = None) -> Path:
+    return (folder or build_dir()) / f"libpae_{name}_{family_hash(name)}.so"
+
+
+def _compile(name: str, target: Path) -> None:
+    nvcc = find_nvcc()
+    source = CSRC / FAMILIES[name][0]
+    partial = target.with_suffix(f".tmp{os.getpid()}.so")
+    command = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(partial), str(source)]
+    say(f"compiling {source.name} for sm_100a ...")
+    started = time.time()
+    process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    while True:
+        try:
+            output, _ = process.communicate(timeout=15)
+            break
+        except subprocess.TimeoutExpired:
+            say(f"... still compiling {source.name} ({int(time.time() - started)} s)")
+    if process.returncode != 0:
+        partial.unlink(missing_ok=True)
+        raise RuntimeError(f"nvcc failed on {source.name}:\n{output}")
+    os.replace(partial, target)
+    say(f"built {target.name} in {time.time() - started:.0f} s")
+
+
+def ensure_built(names: list[str]) -> dict[str, Path]:
+    """Paths of the libraries of the given families, compiling those that are missing."""
+    with _lock:
+        folder = build_dir()
+        paths = {n: library_path(n, folder) for n in names}
+        missing = [n for n in names if not paths[n].is_file()]
+        if missing:
+            errors: list[BaseException] = []
+
+            def work(n: str) -> None:
+                try:
+                    _compile(n, paths[n])
+                except BaseException as exc:  # noqa: BLE001  (reported below)
+                    errors.append(exc)
+
+            threads = [threading.Thread(target=work, args=(n,)) for n in missing]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
+            if errors:
+                raise errors[0]
+        return paths
+
+
+def build_all() -> dict[str, Path]:
+    return ensure_built(list(FAMILIES))

@@ -1,0 +1,211 @@
+"""The kernels as Python functions over torch tensors.
+
+Every function launches hand-written CUDA from `csrc/` on the current stream through
+ctypes. There is no CPU path and no library fallback: without a CUDA device, or when a
+library cannot be built or loaded, a call raises. A kernel that cannot take a size
+refuses it with the message its entry point stored; nothing is retried elsewhere.
+
+Tensors are contiguous; activations and matrices are float32 or bfloat16, biases and
+norm weights float32, indices int32, logits float32.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from . import build
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_libs: dict[str, ctypes.CDLL] = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "paged_attention_engine_b200 runs on a CUDA device only (sm_100a); no device is visible "
+            "and there is no CPU path"
+        )
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = _libs.get(name)
+    if lib is None:
+        require_cuda()
+        path = build.ensure_built([name])[name]
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as exc:
+            raise KernelError(f"cannot load {path}: {exc}") from exc
+        lib.pae_last_error.restype = ctypes.c_char_p
+        _libs[name] = lib
+    return lib
+
+
+def preload(names: list[str]) -> None:
+    """Builds (in parallel) and loads the given families."""
+    require_cuda()
+    build.ensure_built([n for n in names if n not in _libs])
+    for n in names:
+        _lib(n)
+
+
+def _check(lib: ctypes.CDLL, code: int) -> None:
+    if code != 0:
+        raise KernelError(lib.pae_last_error().decode(errors="replace") + f" (code {code})")
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"element type {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _need(t: torch.Tensor, what: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what} is not on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} is {t.dtype}, {dtype} is needed")
+
+
+# ----------------------------------------------------------------------------------- #
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _need(x, "gather_rows: x")
+    _need(rows, "gather_rows: rows", torch.int32)
+    out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_gather_rows(_ptr(out), _ptr(x), _ptr(rows), c_int(rows.numel()), c_int(x.shape[0]),
+                                    c_int(x.shape[1]), c_int(_code(x)), _stream()))
+    return out
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return gather_rows(table, ids)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _need(x, "rms_norm: x")
+    _need(weight, "rms_norm: weight", torch.float32)
+    if weight.numel() != x.shape[-1]:
+        raise KernelError(f"rms_norm: weight of {weight.numel()} for rows of {x.shape[-1]}")
+    out = torch.empty_like(x)
+    lib = _lib("elementwise")
+    rows = x.numel() // x.shape[-1] if x.numel() else 0
+    _check(lib, lib.pae_rms_norm(_ptr(out), _ptr(x), _ptr(weight), c_int(rows), c_int(x.shape[-1]), c_float(eps),
+                                 c_int(_code(x)), _stream()))
+    return out
+
+
+def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
+    """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]."""
+    _need(x, "linear: x")
+    _need(weight, "linear: weight")
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k:
+        raise KernelError(f"linear: x is [{m}, {k}], weight is {tuple(weight.shape)}")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if bias is not None:
+        _need(bias, "linear: bias", torch.float32)
+    if residual is not None:
+        _need(residual, "linear: residual", out_dtype)
+        if tuple(residual.shape) != (m, n):
+            raise KernelError(f"linear: residual is {tuple(residual.shape)}, the product is [{m}, {n}]")
+    lib = _lib("gemm_simt")
+    _check(lib, lib.pae_linear_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
+                                    c_int(k), c_int(_code(x)), c_int(_code(weight)), c_int(_DTYPE_CODE[out_dtype]),
+                                    _stream()))
+    return out
+
+
+def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    _need(positions, "rotary_table: positions", torch.int32)
+    _need(inv_freq, "rotary_table: inv_freq", torch.float32)
+    half = inv_freq.numel()
+    table = torch.empty((positions.numel(), 2 * half), dtype=torch.float32, device=positions.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_rotary_table(_ptr(table), _ptr(positions), _ptr(inv_freq), c_int(positions.numel()),
+                                     c_int(half), _stream()))
+    return table
+
+
+def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_heads, head_dim, page_size) -> None:
+    _need(qkv, "rotary_qk_cache_write: qkv")
+    tokens = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError(f"rotary_qk_cache_write: qkv rows of {qkv.shape[1]} for {num_heads}+2x{num_kv_heads} heads of {head_dim}")
+    if table is not None:
+        _need(table, "rotary_qk_cache_write: table", torch.float32)
+        if tuple(table.shape) != (tokens, head_dim):
+            raise KernelError(f"rotary_qk_cache_write: table is {tuple(table.shape)}, [{tokens}, {head_dim}] is needed")
+    if slots is not None:
+        _need(slots, "rotary_qk_cache_write: slots", torch.int32)
+        _need(keys, "rotary_qk_cache_write: keys", qkv.dtype)
+        _need(values, "rotary_qk_cache_write: values", qkv.dtype)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_rotary_qk_cache_write(
+        _ptr(qkv), _ptr(table), _ptr(slots), _ptr(keys if slots is not None else None),
+        _ptr(values if slots is not None else None), c_int(tokens), c_int(num_heads), c_int(num_kv_heads),
+        c_int(head_dim), c_int(page_size), c_int(_code(qkv)), _stream()))
+
+
+def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
+                    page_size, max_q_len, max_kv_len, scale, window) -> torch.Tensor:
+    _need(qkv, "paged_attention: qkv")
+    _need(keys, "paged_attention: keys", qkv.dtype)
+    _need(values, "paged_attention: values", qkv.dtype)
+    for name, t in (("block_table", block_table), ("q_start", q_start), ("q_pos0", q_pos0), ("kv_len", kv_len)):
+        _need(t, f"paged_attention: {name}", torch.int32)
+    tokens = qkv.shape[0]
+    seqs = kv_len.numel()
+    out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    lib = _lib("attention_simt")
+    _check(lib, lib.pae_paged_attention_simt(
+        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
+        _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads),
+        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(_code(qkv)), _stream()))
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    _need(gate_up, "silu_mul: gate_up")
+    tokens, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"silu_mul: rows of {two_i} do not split into gate and up")
+    out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), c_int(tokens), c_int(two_i // 2), c_int(_code(gate_up)), _stream()))
+    return out
+
+
+def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> torch.Tensor:
+    """int32 [rows]: argmax where temperature is 0, else the Gumbel-max draw of the row's counters."""
+    _need(logits, "sample: logits", torch.float32)
+    _need(temperature, "sample: temperature", torch.float32)
+    for name, t in (("seed_lo", seed_lo), ("seed_hi", seed_hi), ("request_key", request_key), ("output_index", output_index)):
+        _need(t, f"sample: {name}", torch.int32)
+    rows, vocab = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    _check(lib, lib.pae_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
+                               _ptr(request_key), _ptr(output_index), c_int(rows), c_int(vocab), _stream()))
+    return out

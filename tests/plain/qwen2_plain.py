@@ -282,7 +282,7 @@ def gumbel_uniform(seed: int, request_key: int, output_index: int, vocab_index: 
     h = _mix32(h + (request_key & _M32) * 0x7FEB352D)
     h = _mix32(h + (output_index & _M32) * 0x846CA68B)
     h = _mix32(h + (vocab_index & _M32) * 0x9E3779B1)
-    return ((h >> 8) + 0.5) * (1.0 / 16777216.0)
+    return ((h >> 9) + 0.5) * (1.0 / 8388608.0)
 
 
 def sample_scores(logits: torch.Tensor, temperature: float, seed: int, request_key: int, output_index: int):

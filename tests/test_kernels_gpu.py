@@ -1,0 +1,175 @@
+"""Each kernel alone against its plain reference (tests/torch_ops.py), at sizes other than
+the engine's tiny models: widths and vocabularies that are no power of two, head sizes in
+steps of 16, odd numbers of heads and groups, page sizes from 1 up."""
+
+import pytest
+import torch
+
+import torch_ops as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from paged_attention_engine_b200.kernels import ops as kernel_ops
+
+    return kernel_ops
+
+
+def _close(got, want, dtype, scale=1.0):
+    got, want = got.float().cpu(), want.float().cpu()
+    limit = (2e-5 if dtype == torch.float32 else 2.0 ** -7) * max(1.0, float(want.abs().max())) * scale
+    gap = (got - want).abs().max().item()
+    assert gap <= limit, f"max gap {gap:.3e} > {limit:.3e}"
+
+
+def _rand(shape, dtype, seed, std=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=gen) * std).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width", [(1, 8), (7, 100), (33, 1536), (5, 4104)])
+def test_rms_norm(ops, dtype, rows, width):
+    x = _rand((rows, width), dtype, 1, 3.0)
+    w = (1 + 0.1 * torch.randn(width)).cuda()
+    _close(ops.rms_norm(x, w, 1e-5), ref.rms_norm(x.cpu(), w.cpu(), 1e-5), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gather_and_embedding(ops, dtype):
+    table = _rand((301, 72), dtype, 2)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32).cuda()
+    assert torch.equal(ops.embedding(ids, table).cpu(), table.cpu()[ids.cpu().long()])
+    assert torch.equal(ops.gather_rows(table, ids[:2]).cpu(), table.cpu()[[0, 300]])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 509, 96), (5, 64, 176), (70, 130, 257), (129, 1536, 1536), (8, 3001, 520)])
+@pytest.mark.parametrize("extras", ["plain", "bias", "bias+residual"])
+def test_linear(ops, dtype, m, n, k, extras):
+    x = _rand((m, k), dtype, 3)
+    w = _rand((n, k), dtype, 4, 0.05)
+    bias = torch.randn(n).cuda() if "bias" in extras else None
+    res = _rand((m, n), dtype, 5) if "residual" in extras else None
+    want = ref.linear(x.cpu(), w.cpu(), None if bias is None else bias.cpu(), None if res is None else res.cpu())
+    _close(ops.linear(x, w, bias, res), want, dtype)
+
+
+def test_linear_mixed_types(ops):
+    x = _rand((9, 200), torch.bfloat16, 6)
+    w32 = _rand((77, 200), torch.float32, 7, 0.05)
+    w16 = w32.to(torch.bfloat16)
+    _close(ops.linear(x, w32), ref.linear(x.cpu(), w32.cpu()), torch.bfloat16)
+    out = ops.linear(x, w16, out_dtype=torch.float32)
+    assert out.dtype == torch.float32
+    _close(out, ref.linear(x.cpu().float(), w16.cpu().float()), torch.float32)
+
+
+def test_linear_rows_do_not_depend_on_the_batch(ops):
+    """A token's product is the same bits whether it runs alone or among others."""
+    x = _rand((37, 300), torch.float32, 8)
+    w = _rand((190, 300), torch.float32, 9, 0.05)
+    whole = ops.linear(x, w)
+    for r in (0, 13, 36):
+        assert torch.equal(ops.linear(x[r : r + 1].contiguous(), w)[0], whole[r])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    gu = _rand((11, 2 * 173), dtype, 10, 4.0)
+    _close(ops.silu_mul(gu), ref.silu_mul(gu.cpu()), dtype)
+
+
+@pytest.mark.parametrize("theta,half", [(1e4, 8), (1e6, 64)])
+def test_rotary_table(ops, theta, half):
+    positions = torch.tensor([0, 1, 2, 77, 4095, 32767], dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (theta ** (torch.arange(0, 2 * half, 2).float() / (2 * half)))).cuda()
+    got = ops.rotary_table(positions, inv_freq).cpu()
+    angle = positions.cpu().float()[:, None] * inv_freq.cpu()[None, :]
+    want = torch.cat((angle.double().cos(), angle.double().sin()), dim=-1).float()
+    assert (got - want).abs().max().item() <= 2e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(4, 2, 16, 4), (3, 1, 32, 16), (7, 7, 48, 1), (12, 2, 128, 16)])
+def test_rotary_and_cache_write(ops, dtype, heads, kv_heads, d, page):
+    tokens, pages = 19, 9
+    qkv = _rand((tokens, (heads + 2 * kv_heads) * d), dtype, 11)
+    positions = torch.arange(100, 100 + tokens, dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))).cuda()
+    table = ops.rotary_table(positions, inv_freq)
+    slots = torch.randperm(pages * page)[:tokens].to(torch.int32) if pages * page >= tokens else None
+    if slots is None:
+        pages = tokens
+        slots = torch.randperm(pages * page)[:tokens].to(torch.int32)
+    keys = torch.zeros(pages, kv_heads, page, d, dtype=dtype).cuda()
+    values = torch.zeros_like(keys)
+    want_qkv, want_k, want_v = qkv.cpu().clone(), keys.cpu().clone(), values.cpu().clone()
+    ref.rotary_qk_cache_write(want_qkv, table.cpu(), slots, want_k, want_v, heads, kv_heads, d, page)
+    ops.rotary_qk_cache_write(qkv, table, slots.cuda(), keys, values, heads, kv_heads, d, page)
+    _close(qkv, want_qkv, dtype)
+    _close(keys, want_k, dtype)
+    _close(values, want_v, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize(
+    "heads,kv_heads,d,page,window",
+    [(4, 2, 16, 4, 0), (3, 1, 32, 16, 0), (5, 5, 48, 8, 24), (6, 3, 64, 1, 0), (12, 2, 128, 16, 0), (2, 1, 256, 32, 40)],
+)
+def test_paged_attention(ops, dtype, heads, kv_heads, d, page, window):
+    """Portions at offsets, single tokens and whole prompts in one batch, over shuffled pages."""
+    gen = torch.Generator().manual_seed(12)
+    q_lens = [1, 37, 5, 1, 64]
+    pos0 = [70, 0, 29, 0, 101]
+    kv_lens = [p + n for p, n in zip(pos0, q_lens)]
+    width = max(-(-n // page) for n in kv_lens)
+    total_pages = sum(-(-n // page) for n in kv_lens) + 3
+    order = torch.randperm(total_pages, generator=gen).tolist()
+    table = torch.full((len(q_lens), width), -1, dtype=torch.int32)
+    for b, n in enumerate(kv_lens):
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+    keys = (torch.randn(total_pages, kv_heads, page, d, generator=gen)).to(dtype)
+    values = (torch.randn(total_pages, kv_heads, page, d, generator=gen)).to(dtype)
+    # One far key per request gets a large score, so that missing it cannot hide.
+    qkv = torch.randn(sum(q_lens), (heads + 2 * kv_heads) * d, generator=gen).to(dtype)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5 * 3.0, window=window)
+    tensors = [qkv, keys, values, table, q_start, torch.tensor(pos0, dtype=torch.int32), torch.tensor(kv_lens, dtype=torch.int32)]
+    want = ref.paged_attention(*tensors, **args)
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    _close(got, want, dtype, scale=2.0)
+
+
+@pytest.mark.parametrize("vocab", [5, 509, 151936])
+def test_sampling(ops, vocab):
+    gen = torch.Generator().manual_seed(13)
+    rows = 6
+    logits = torch.randn(rows, vocab, generator=gen)
+    logits[0, vocab // 2] = logits[0, vocab - 1] = 9.0        # a tie: the lower index wins
+    temperature = torch.tensor([0.0, 0.0, 0.7, 1.0, 1.3, 0.7])
+    seed = torch.tensor([1, 1, 1, 2**40 + 5, 7, 1], dtype=torch.int64)
+    key = torch.tensor([0, 1, 2, 3, 4, 2], dtype=torch.int32)
+    index = torch.tensor([0, 0, 5, 6, 7, 5], dtype=torch.int32)
+    lo = (seed & 0xFFFFFFFF).to(torch.int64)
+    lo = torch.where(lo >= 2**31, lo - 2**32, lo).to(torch.int32)
+    hi = (seed >> 32).to(torch.int32)
+    got = ops.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), key.cuda(), index.cuda()).cpu()
+    assert got[0].item() == vocab // 2
+    assert got[1].item() == int(torch.argmax(logits[1]))
+    logits[5] = logits[2]
+    got2 = ops.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), key.cuda(), index.cuda()).cpu()
+    assert got2[5] == got2[2], "the same counters and logits draw the same token whatever the row"
+    # The device's float32 scores may order two near-equal candidates otherwise than the
+    # float64 restatement: the token drawn must score within 1e-4 of the restatement's best.
+    from plain import qwen2_plain as plain
+    if vocab <= 509:
+        for r in range(2, 5):
+            scores = plain.sample_scores(logits[r], float(temperature[r]), int(seed[r]), int(key[r]), int(index[r]))
+            assert scores[got[r]].item() >= scores.max().item() - 1e-4

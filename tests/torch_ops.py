@@ -123,7 +123,7 @@ def sample(logits, temperature, seed, request_key, output_index):
             h = _mix32(h + (int(request_key[r]) & _M32) * 0x7FEB352D)
             h = _mix32(h + (int(output_index[r]) & _M32) * 0x846CA68B)
             hv = _mix32((h + ((vocab * 0x9E3779B1) & _M32)) & _M32)
-            u = ((hv >> 8).double() + 0.5) / 16777216.0
+            u = ((hv >> 9).double() + 0.5) / 8388608.0
             row = row / t - torch.log(-torch.log(u))
         out[r] = int(torch.argmax(row))
     return out
