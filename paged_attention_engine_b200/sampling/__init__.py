@@ -1,0 +1,3 @@
+from .sampler import Sampler, SamplingRow
+
+__all__ = ["Sampler", "SamplingRow"]

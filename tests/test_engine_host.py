@@ -69,3 +69,52 @@ def test_one_traversal_per_step(tiny):
         folder, "float32", trace, helpers.max_live_tokens(trace), page, ops=torch_ops, device="cpu"
     )
     assert replayer.runner.model.forward_pass_count == len(trace)
+
+
+def test_entry_point_generates_what_the_plain_implementation_does(tmp_path):
+    """Requests through LLM (scheduler, executor, sampler, cache manager) on stand-in
+    kernels: greedy tokens equal the plain implementation's, under a pool so small that
+    requests are preempted and recomputed, and under a token budget that cuts prompts."""
+    from paged_attention_engine_b200 import LLM, Engine, Request
+    from plain import qwen2_plain as plain
+
+    raw, page, seed = helpers.TINY["tiny_a"]
+    folder = helpers.write_model(tmp_path / "m", raw, seed, torch.float32, sharpen=4.0)
+    engine = Engine.from_pretrained(folder, "float32", device="cpu", ops=torch_ops)
+    llm = LLM(engine, num_blocks=14, block_size=page, max_num_seqs=4, max_num_batched_tokens=12, record_logits=True)
+    prompts = [helpers.random_tokens(256, n, 40 + n) for n in (5, 11, 17, 3)]
+    for i, prompt in enumerate(prompts):
+        assert llm.add_request(Request(f"p{i}", tuple(prompt), 8))
+    out = llm.run_to_completion()
+    cfg, weights = plain.read_config(folder), plain.read_weights(folder)
+    for i, prompt in enumerate(prompts):
+        want, rows = plain.generate_greedy(prompt, 8, weights, cfg)
+        assert list(out[f"p{i}"]) == want
+        got_rows = torch.stack(llm.scheduler.finished[f"p{i}"].step_logits)
+        assert (got_rows - rows).abs().max().item() <= helpers.tolerance(torch.float32, rows)
+    from paged_attention_engine_b200 import EventKind
+    assert llm.scheduler.events_of(EventKind.PREEMPT), "14 pages of 4 tokens cannot hold four such requests"
+    assert llm.runner.model.forward_pass_count == llm.scheduler._step
+
+
+def test_temperature_sampling_does_not_depend_on_the_batch(tmp_path):
+    from paged_attention_engine_b200 import LLM, Engine, Request
+
+    raw, page, seed = helpers.TINY["tiny_b"]
+    folder = helpers.write_model(tmp_path / "m", raw, seed, torch.float32)
+    engine = Engine.from_pretrained(folder, "float32", device="cpu", ops=torch_ops)
+    prompts = {f"t{i}": tuple(helpers.random_tokens(509, n, 60 + n)) for i, n in enumerate((1, 7, 23))}
+
+    def run(**options):
+        llm = LLM(engine, block_size=page, **options)
+        for rid, prompt in prompts.items():
+            llm.add_request(Request(rid, prompt, 6, temperature=0.8, seed=1234))
+        return llm.run_to_completion()
+
+    together = run(num_blocks=64)
+    alone = run(num_blocks=64, max_num_seqs=1)
+    squeezed = run(num_blocks=5, max_num_batched_tokens=5)
+    assert together == alone == squeezed
+    greedy = LLM(engine, num_blocks=64, block_size=page)
+    greedy.add_request(Request("t2", prompts["t2"], 6))
+    assert greedy.run_to_completion()["t2"] != together["t2"]

@@ -109,7 +109,7 @@ def _mix32(x):
     return x
 
 
-def sample(logits, temperature, seed, request_key, output_index):
+def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index):
     """Per row: argmax for temperature 0, else Gumbel-max with the engine's counter-based noise."""
     out = torch.empty(logits.shape[0], dtype=torch.int32)
     vocab = torch.arange(logits.shape[1], dtype=torch.int64)
@@ -117,9 +117,8 @@ def sample(logits, temperature, seed, request_key, output_index):
         t = float(temperature[r])
         row = logits[r].double().cpu()
         if t > 0.0:
-            s = int(seed[r]) & 0xFFFFFFFFFFFFFFFF
-            h = _mix32((s & _M32) ^ 0x9E3779B9)
-            h = _mix32(h ^ ((s >> 32) & _M32))
+            h = _mix32((int(seed_lo[r]) & _M32) ^ 0x9E3779B9)
+            h = _mix32(h ^ (int(seed_hi[r]) & _M32))
             h = _mix32(h + (int(request_key[r]) & _M32) * 0x7FEB352D)
             h = _mix32(h + (int(output_index[r]) & _M32) * 0x846CA68B)
             hv = _mix32((h + ((vocab * 0x9E3779B1) & _M32)) & _M32)
