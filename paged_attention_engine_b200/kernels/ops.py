@@ -21,6 +21,9 @@ from . import build
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _libs: dict[str, ctypes.CDLL] = {}
 
+# Kernel launches made through this module since import (read by the measurement script).
+launches = 0
+
 
 class KernelError(RuntimeError):
     pass
@@ -56,7 +59,9 @@ def preload(names: list[str]) -> None:
         _lib(n)
 
 
-def _check(lib: ctypes.CDLL, code: int) -> None:
+def _check(lib: ctypes.CDLL, code: int, count: int = 1) -> None:
+    global launches
+    launches += count
     if code != 0:
         raise KernelError(lib.pae_last_error().decode(errors="replace") + f" (code {code})")
 
