@@ -1,0 +1,533 @@
+// Matrix products of the bfloat16 path on the fifth-generation tensor cores (sm_100a):
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle),
+// tcgen05.mma issued by one thread with the accumulator in tensor memory, tcgen05.ld for
+// the epilogue. No cluster multicast is used anywhere.
+//
+// Both operands are K-major ([rows, K] row-major, K contiguous), which is how activations
+// [tokens, K] and checkpoint weights [out, K] lie in memory (the reference calls
+// F.linear on the same layout, engine/model.py:303-320). One kernel serves two shapes of
+// work:
+//
+//   NORMAL   many tokens (a prompt's portion): the 128 rows of the MMA are tokens, the
+//            BN columns are weight rows. out[token, n] = acc (+ bias[n]) (+ residual).
+//   SWAPPED  few tokens (decoding): the 128 rows of the MMA are weight rows, the BN >= T
+//            columns are the tokens, so a step with 1..64 tokens streams every weight once
+//            at full MMA width. K is split over blockIdx.z so that enough blocks are in
+//            flight to fill the memory system; each split writes float32 partial sums
+//            partial[split, token, n], and the kernel that follows sums them in a fixed
+//            order (with bias, residual, or whatever it fuses).
+//
+// One block computes one 128 x BN tile over its K range. Warp 0 issues the TMA loads,
+// warp 1 allocates tensor memory and issues the MMAs, warps 2-5 run the epilogue (each
+// reads the 32 lanes of tensor memory that its warp id modulo 4 may touch). Every
+// mbarrier wait is bounded: when one gives up it records a code in `error`, the roles
+// leave their loops, loads in flight are waited for (bounded again), tensor memory is
+// freed and the block returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+using namespace pae;
+
+namespace {
+
+constexpr int BM = 128;          // MMA rows per tile
+constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 21;
+
+enum Mode : int { NORMAL = 0, SWAPPED = 1 };
+
+struct Params {
+  void* out;
+  const float* bias;
+  const void* residual;
+  int rows_a;        // rows of the A operand (tokens in NORMAL, weight rows in SWAPPED)
+  int rows_b;        // rows of the B operand
+  int k_blocks;      // ceil(K / 64)
+  int kb_per_split;
+  int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
+  int out_f32;
+  int* error;
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
+// Waits for a phase of an mbarrier, at most WAIT_LIMIT polls. On giving up it raises the
+// block's abort flag and records `code`; it also returns false as soon as another role
+// has raised the flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (i > 64) __nanosleep(64);
+  }
+  *abort_flag = 1;
+  atomicCAS(error, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem]^T, both K-major, one thread issues.
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 16 consecutive float32 columns of this thread's lane of tensor memory.
+__device__ __forceinline__ void tmem_load16(uint32_t address, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(address)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
+// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), leading byte offset 1
+// (unused with a swizzle), descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
+  uint64_t d = 0;
+  d |= (uint64_t)((address & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor: float32 accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9
+// and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN>
+struct Tile {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // As many stages as fit beside a second resident block (about 100 KB each), at most 8.
+  static constexpr int STAGES = (100 * 1024 / STAGE_BYTES) > 8 ? 8 : (100 * 1024 / STAGE_BYTES < 2 ? 2 : 100 * 1024 / STAGE_BYTES);
+  static constexpr int TMEM_COLUMNS = BN < 32 ? 32 : BN;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_b, const Params p) {
+  using T = Tile<BN>;
+  extern __shared__ uint8_t raw_smem[];
+  const uint32_t raw = smem_u32(raw_smem);
+  const uint32_t base = (raw + 1023u) & ~1023u;                   // swizzled tiles start on 1024 bytes
+  uint8_t* generic_base = raw_smem + (base - raw);
+  const uint32_t bars = base + T::STAGES * T::STAGE_BYTES;        // full[STAGES], empty[STAGES], tmem_full
+  volatile uint32_t* tmem_holder = (volatile uint32_t*)(generic_base + T::STAGES * T::STAGE_BYTES + 8 * (2 * T::STAGES + 1));
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_a = blockIdx.x, tile_b = blockIdx.y;
+  const int kb_begin = blockIdx.z * p.kb_per_split;
+  const int kb_end = min(p.k_blocks, kb_begin + p.kb_per_split);
+  const int kb_count = kb_end - kb_begin;
+
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (T::STAGES + s); };
+  const uint32_t tmem_full_bar = bars + 8u * (2 * T::STAGES);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_holder), T::TMEM_COLUMNS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % T::STAGES;
+        if (i >= T::STAGES && !mbar_wait(empty_bar(s), ((i / T::STAGES) - 1) & 1, abort_flag, p.error, 1)) break;
+        const uint32_t a_dst = base + s * T::STAGE_BYTES;
+        mbar_expect_tx(full_bar(s), T::STAGE_BYTES);
+        tma_load_2d(a_dst, &map_a, full_bar(s), (kb_begin + i) * BK, tile_a * BM);
+        tma_load_2d(a_dst + T::A_BYTES, &map_b, full_bar(s), (kb_begin + i) * BK, tile_b * BN);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // Loads that were issued still write into this block's shared memory: wait for them.
+        for (int i = max(0, issued - T::STAGES); i < issued; ++i)
+          for (uint32_t t = 0; t < WAIT_LIMIT && !mbar_try_wait(full_bar(i % T::STAGES), (i / T::STAGES) & 1); ++t) __nanosleep(64);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = instruction_descriptor(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % T::STAGES;
+        ok = mbar_wait(full_bar(s), (i / T::STAGES) & 1, abort_flag, p.error, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t a_addr = base + s * T::STAGE_BYTES;
+        const uint32_t b_addr = a_addr + T::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          // Inside the 128-byte swizzle row a step of 16 elements is 32 bytes.
+          umma_bf16(tmem_base, smem_descriptor(a_addr + k * UMMA_K * 2), smem_descriptor(b_addr + k * UMMA_K * 2), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(empty_bar(s));      // the stage is free once these MMAs have read it
+      }
+      if (ok) tcgen05_commit(tmem_full_bar);  // the accumulator is complete once all MMAs are done
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quadrant = warp & 3;                  // the tensor-memory lanes this warp may read
+    const int row_in_tile = quadrant * 32 + lane;
+    bool ok = true;
+    if (kb_count > 0) ok = mbar_wait(tmem_full_bar, 0, abort_flag, p.error, 3);
+    ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below needs the whole warp
+    tcgen05_fence_after();
+    if (ok) {
+      const int row = tile_a * BM + row_in_tile;    // row of the A operand
+      const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (kb_count > 0) {
+          tmem_load16(lane_address + c0, v);        // warp-collective: every lane takes part
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        const int col0 = tile_b * BN + c0;          // row of the B operand
+        if (row >= p.rows_a || col0 >= p.rows_b) continue;
+        if (MODE == SWAPPED) {
+          // partial[split, token, weight row]: for one token the 32 lanes write 32 neighbours.
+          float* out = (float*)p.out + (size_t)blockIdx.z * p.rows_b * p.ld_out;
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (col0 + i < p.rows_b) out[(size_t)(col0 + i) * p.ld_out + row] = v[i];
+        } else {
+          const int valid = min(16, p.rows_b - col0);
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (i < valid) v[i] += p.bias[col0 + i];
+          }
+          const size_t at = (size_t)row * p.ld_out + col0;
+          if (p.out_f32) {
+            float* out = (float*)p.out + at;
+            if (p.residual != nullptr) {
+              const float* res = (const float*)p.residual + at;
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < valid) v[i] += res[i];
+            }
+            if (valid == 16 && (at & 3) == 0) {
+#pragma unroll
+              for (int i = 0; i < 16; i += 4) *(float4*)(out + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < valid) out[i] = v[i];
+            }
+          } else {
+            __nv_bfloat16* out = (__nv_bfloat16*)p.out + at;
+            if (p.residual != nullptr) {
+              const __nv_bfloat16* res = (const __nv_bfloat16*)p.residual + at;
+              if (valid == 16 && (at & 7) == 0) {
+                uint4 r0 = *(const uint4*)res, r1 = *(const uint4*)(res + 8);
+                const __nv_bfloat16* rr0 = (const __nv_bfloat16*)&r0;
+                const __nv_bfloat16* rr1 = (const __nv_bfloat16*)&r1;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  v[i] += __bfloat162float(rr0[i]);
+                  v[8 + i] += __bfloat162float(rr1[i]);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                  if (i < valid) v[i] += __bfloat162float(res[i]);
+              }
+            }
+            if (valid == 16 && (at & 7) == 0) {
+              uint4 w0, w1;
+              __nv_bfloat162* h0 = (__nv_bfloat162*)&w0;
+              __nv_bfloat162* h1 = (__nv_bfloat162*)&w1;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+              }
+              *(uint4*)out = w0;
+              *(uint4*)(out + 8) = w1;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                if (i < valid) out[i] = __float2bfloat16_rn(v[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, T::TMEM_COLUMNS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side: tensor maps (cached by pointer and shape), launch.
+// ---------------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled() {
+  static EncodeTiled fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return (EncodeTiled)ptr;
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int rows, k, box_rows;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& key) const {
+    size_t h = (size_t)key.ptr;
+    h = h * 1000003u ^ (size_t)key.rows;
+    h = h * 1000003u ^ (size_t)key.k;
+    return h * 1000003u ^ (size_t)key.box_rows;
+  }
+};
+
+// A [rows, k] bfloat16 row-major matrix as boxes of 64 elements x box_rows rows, 128-byte
+// swizzle, zero fill outside the matrix.
+int tensor_map(CUtensorMap* out, const void* ptr, int rows, int k, int box_rows) {
+  static std::mutex mutex;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  std::lock_guard<std::mutex> guard(mutex);
+  const MapKey key{ptr, rows, k, box_rows};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return 0;
+  }
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return fail(101, "linear_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t element_strides[2] = {1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, element_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(102, "linear_tcgen05: cuTensorMapEncodeTiled failed with %d for [%d, %d]", (int)r, rows, k);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int BN, int MODE>
+int launch(const Params& p, const void* a, const void* b, int k, int splits, cudaStream_t stream) {
+  using T = Tile<BN>;
+  CUtensorMap map_a, map_b;
+  if (int err = tensor_map(&map_a, a, p.rows_a, k, BM)) return err;
+  if (int err = tensor_map(&map_b, b, p.rows_b, k, BN)) return err;
+  auto kernel = gemm_tcgen05_kernel<BN, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_BYTES);
+    if (err != cudaSuccess) return fail(100, "linear_tcgen05: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  dim3 grid((p.rows_a + BM - 1) / BM, (p.rows_b + BN - 1) / BN, splits);
+  kernel<<<grid, THREADS, T::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return check_launch("linear_tcgen05");
+}
+
+int check_operands(const void* x, const void* w, int k) {
+  if (k % 8) return fail(2, "linear_tcgen05: K = %d is not a multiple of 8 (a TMA row pitch must be a multiple of 16 bytes)", k);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(2, "linear_tcgen05: an operand does not start on a 16-byte boundary");
+  return 0;
+}
+
+}  // namespace
+
+// out[tokens, n] = x[tokens, k] . w[n, k]^T (+ bias[n]) (+ residual[tokens, n]); x, w, residual
+// bfloat16, bias float32, out bfloat16 or float32 (then residual is float32 too).
+PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const float* bias, const void* residual,
+                                  int tokens, int n, int k, int out_f32, int* error, void* stream) {
+  if (tokens == 0 || n == 0) return 0;
+  if (int err = check_operands(x, w, k)) return err;
+  Params p{};
+  p.out = out;
+  p.bias = bias;
+  p.residual = residual;
+  p.rows_a = tokens;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = p.k_blocks;
+  p.ld_out = n;
+  p.out_f32 = out_f32;
+  p.error = error;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (n >= 128) return launch<128, NORMAL>(p, x, w, k, 1, s);
+  if (n > 32) return launch<64, NORMAL>(p, x, w, k, 1, s);
+  return launch<32, NORMAL>(p, x, w, k, 1, s);
+}
+
+// How many float32 partial planes `pae_linear_tcgen05_swapped` writes for this shape.
+PAE_EXPORT int pae_linear_swapped_splits(int n, int k) {
+  const int tiles = (n + BM - 1) / BM;
+  const int k_blocks = (k + BK - 1) / BK;
+  int splits = (2 * 148 + tiles - 1) / tiles;          // about two blocks for each of the 148 SMs
+  splits = splits < 1 ? 1 : splits;
+  const int most = k_blocks / 2 < 1 ? 1 : k_blocks / 2;  // at least two k-blocks per split
+  splits = splits > most ? most : splits;
+  const int per = (k_blocks + splits - 1) / splits;
+  return (k_blocks + per - 1) / per;
+}
+
+// partial[split, token, n] (float32) = x[tokens, k_split] . w[n, k_split]^T for tokens <= 64.
+PAE_EXPORT int pae_linear_tcgen05_swapped(float* partial, const void* x, const void* w, int tokens, int n, int k,
+                                          int* error, void* stream) {
+  if (tokens == 0 || n == 0) return 0;
+  if (tokens > 64) return fail(2, "linear_tcgen05_swapped: %d tokens are more than the 64 it takes", tokens);
+  if (int err = check_operands(x, w, k)) return err;
+  const int splits = pae_linear_swapped_splits(n, k);
+  Params p{};
+  p.out = partial;
+  p.rows_a = n;
+  p.rows_b = tokens;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+  p.ld_out = n;
+  p.out_f32 = 1;
+  p.error = error;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (tokens <= 16) return launch<16, SWAPPED>(p, w, x, k, splits, s);
+  if (tokens <= 32) return launch<32, SWAPPED>(p, w, x, k, splits, s);
+  return launch<64, SWAPPED>(p, w, x, k, splits, s);
+}
+
+// out[token, n] = sum over splits of partial[split, token, n] (+ bias[n]) (+ residual[token, n]),
+// summed in the order of the splits. out and residual bfloat16 or float32.
+template <typename TO>
+__global__ void reduce_splits_kernel(TO* __restrict__ out, const float* __restrict__ partial, const float* __restrict__ bias,
+                                     const TO* __restrict__ residual, int splits, long long plane, int n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= plane) return;
+  float v = 0.f;
+  for (int s = 0; s < splits; ++s) v += partial[(size_t)s * plane + i];
+  if (bias != nullptr) v += bias[i % n];
+  if (residual != nullptr) v += to_float(residual[i]);
+  out[i] = from_float<TO>(v);
+}
+
+PAE_EXPORT int pae_reduce_splits(void* out, const float* partial, const float* bias, const void* residual, int splits,
+                                 int tokens, int n, int out_f32, void* stream) {
+  const long long plane = (long long)tokens * n;
+  if (plane == 0) return 0;
+  const unsigned blocks = (unsigned)((plane + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_f32)
+    reduce_splits_kernel<float><<<blocks, 256, 0, s>>>((float*)out, partial, bias, (const float*)residual, splits, plane, n);
+  else
+    reduce_splits_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, partial, bias, (const __nv_bfloat16*)residual, splits, plane, n);
+  return check_launch("reduce_splits");
+}
+
+PAE_DEFINE_LAST_ERROR()

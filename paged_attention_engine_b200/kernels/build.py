@@ -35,6 +35,7 @@ FAMILIES: dict[str, list[str]] = {
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "attention_simt": ["attention_simt.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
+    "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
 }
 
 _lock = threading.Lock()

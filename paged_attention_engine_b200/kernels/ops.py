@@ -119,6 +119,46 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+# The bfloat16 products run on the tcgen05 kernels when the shape allows; set to False to
+# send everything to the CUDA-core kernel (tests compare the two).
+use_tensor_cores = True
+SWAPPED_MAX_TOKENS = 64
+
+_error_flags: dict[int, torch.Tensor] = {}
+
+
+def _error_flag(device: torch.device) -> torch.Tensor:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    flag = _error_flags.get(index)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_flags[index] = flag
+    return flag
+
+
+def check_device_errors() -> None:
+    """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
+    for index, flag in _error_flags.items():
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise KernelError(
+                f"a tcgen05 kernel on device {index} gave up waiting on an mbarrier (role code {code}); "
+                "its output is not valid"
+            )
+
+
+def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
+    return (
+        use_tensor_cores
+        and x.dtype == torch.bfloat16
+        and weight.dtype == torch.bfloat16
+        and x.shape[1] % 8 == 0
+        and x.data_ptr() % 16 == 0
+        and weight.data_ptr() % 16 == 0
+    )
+
+
 def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]."""
     _need(x, "linear: x")
@@ -128,17 +168,44 @@ def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     if weight.shape[1] != k:
         raise KernelError(f"linear: x is [{m}, {k}], weight is {tuple(weight.shape)}")
     out_dtype = out_dtype or x.dtype
-    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     if bias is not None:
         _need(bias, "linear: bias", torch.float32)
     if residual is not None:
         _need(residual, "linear: residual", out_dtype)
         if tuple(residual.shape) != (m, n):
             raise KernelError(f"linear: residual is {tuple(residual.shape)}, the product is [{m}, {n}]")
+    if m == 0:
+        return torch.empty((m, n), dtype=out_dtype, device=x.device)
+    if _tensor_core_shape(x, weight, residual, out_dtype):
+        return _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     lib = _lib("gemm_simt")
     _check(lib, lib.pae_linear_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
                                     c_int(k), c_int(_code(x)), c_int(_code(weight)), c_int(_DTYPE_CODE[out_dtype]),
                                     _stream()))
+    return out
+
+
+def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch.Tensor:
+    lib = _lib("gemm_tcgen05")
+    flag = _error_flag(x.device)
+    out_f32 = c_int(1 if out_dtype == torch.float32 else 0)
+    if m <= SWAPPED_MAX_TOKENS:
+        # Few tokens: weight rows fill the MMA's 128 rows, K is split, partial sums are
+        # float32 scratch that the reduction (or nothing, for one split) turns into the output.
+        splits = lib.pae_linear_swapped_splits(c_int(n), c_int(k))
+        partial = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
+        _check(lib, lib.pae_linear_tcgen05_swapped(_ptr(partial), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
+                                                   _ptr(flag), _stream()))
+        if splits == 1 and bias is None and residual is None and out_dtype == torch.float32:
+            return partial[0]
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(partial), _ptr(bias), _ptr(residual), c_int(splits), c_int(m),
+                                          c_int(n), out_f32, _stream()))
+        return out
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
+                                       c_int(k), out_f32, _ptr(flag), _stream()))
     return out
 
 
