@@ -55,6 +55,7 @@ class StepContext:
     logit_rows: torch.Tensor      # int32 [wanted]: token rows whose logits are wanted
     max_q_len: int
     max_kv_len: int
+    num_single: int               # entries that bring exactly one token
     groups: list[GroupStep]
     # Host copies, for parts (and tests) that plan on the host.
     host_q_lens: list[int] = field(default_factory=list)
@@ -183,6 +184,6 @@ class BatchBuilder:
             ops=self.ops, dtype=self.dtype, device=self.device, num_tokens=total, num_seqs=b,
             token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
             kv_len=part(5), state_slot=part(6), logit_rows=part(7),
-            max_q_len=max(q_lens), max_kv_len=max_kv, groups=groups,
+            max_q_len=max(q_lens), max_kv_len=max_kv, num_single=sum(1 for n in q_lens if n == 1), groups=groups,
             host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
         )

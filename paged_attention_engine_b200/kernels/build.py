@@ -36,6 +36,7 @@ FAMILIES: dict[str, list[str]] = {
     "attention_simt": ["attention_simt.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
+    "attention_mma": ["attention_mma.cu", "common.cuh"],
 }
 
 _lock = threading.Lock()

@@ -47,6 +47,8 @@ def _lib(name: str) -> ctypes.CDLL:
         except OSError as exc:
             raise KernelError(f"cannot load {path}: {exc}") from exc
         lib.pae_last_error.restype = ctypes.c_char_p
+        if name == "attention_mma":
+            lib.pae_decode_scratch_floats.restype = ctypes.c_longlong
         _libs[name] = lib
     return lib
 
@@ -240,8 +242,20 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         c_int(head_dim), c_int(page_size), c_int(_code(qkv)), _stream()))
 
 
+def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int) -> tuple[int, int]:
+    """(keys per slice, slices) for the decode kernel: enough (request, kv head, slice) warps to
+    fill 148 SMs about twelve warps deep, slices of at least 32 keys in steps of 16."""
+    wanted = max(1, min(64, -(-2048 // max(1, seqs * kv_heads))))
+    slice_keys = max(32, -(-(-(-max_kv_len // wanted)) // 16) * 16)
+    max_slices = -(-(max_kv_len + 15) // slice_keys)
+    return slice_keys, max_slices
+
+
 def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
-                    page_size, max_q_len, max_kv_len, scale, window) -> torch.Tensor:
+                    page_size, max_q_len, max_kv_len, scale, window, num_single=None) -> torch.Tensor:
+    """Attention of every token of the step over its request's pages. `num_single` is the number
+    of requests that bring exactly one token when the caller knows it (it decides which kernels
+    are launched; None launches whatever may be needed)."""
     _need(qkv, "paged_attention: qkv")
     _need(keys, "paged_attention: keys", qkv.dtype)
     _need(values, "paged_attention: values", qkv.dtype)
@@ -250,6 +264,26 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     tokens = qkv.shape[0]
     seqs = kv_len.numel()
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    if qkv.dtype == torch.bfloat16 and use_tensor_cores:
+        lib = _lib("attention_mma")
+        if lib.pae_attention_mma_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
+            singles = num_single if num_single is not None else (seqs if max_q_len == 1 else -1)
+            if max_q_len > 1:
+                _check(lib, lib.pae_paged_attention_prefill(
+                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
+                    _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads),
+                    c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
+                    c_int(1), _stream()))
+            if singles != 0:
+                slice_keys, max_slices = decode_slicing(seqs if singles < 0 else singles, num_kv_heads, max_kv_len)
+                floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
+                scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+                _check(lib, lib.pae_paged_attention_decode(
+                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
+                    _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+                    c_int(page_size), c_float(scale), c_int(window), c_int(slice_keys), c_int(max_slices),
+                    _ptr(scratch), _stream()), 2)
+            return out
     lib = _lib("attention_simt")
     _check(lib, lib.pae_paged_attention_simt(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),

@@ -173,3 +173,80 @@ def test_sampling(ops, vocab):
         for r in range(2, 5):
             scores = plain.sample_scores(logits[r], float(temperature[r]), int(seed[r]), int(key[r]), int(index[r]))
             assert scores[got[r]].item() >= scores.max().item() - 1e-4
+
+
+def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True):
+    """Random queries, keys and values over shuffled pages. With `spike`, one far key of every
+    request (its key 3) is made to score high for every query, so that missing it shows."""
+    kv_lens = [p + n for p, n in zip(pos0, q_lens)]
+    width = max(-(-n // page) for n in kv_lens)
+    total_pages = sum(-(-n // page) for n in kv_lens) + 5
+    order = torch.randperm(total_pages, generator=gen).tolist()
+    table = torch.full((len(q_lens), width), -1, dtype=torch.int32)
+    for b, n in enumerate(kv_lens):
+        for i in range(-(-n // page)):
+            table[b, i] = order.pop()
+    keys = torch.randn(total_pages, kv_heads, page, d, generator=gen)
+    values = torch.randn(total_pages, kv_heads, page, d, generator=gen)
+    qkv = torch.randn(sum(q_lens), (heads + 2 * kv_heads) * d, generator=gen)
+    if spike:
+        direction = torch.randn(d, generator=gen)
+        direction /= direction.norm()
+        q_view = qkv.view(sum(q_lens), heads + 2 * kv_heads, d)
+        q_view[:, :heads] += 3.0 * direction
+        for b, n in enumerate(kv_lens):
+            j = min(3, n - 1)
+            keys[table[b, j // page], :, j % page] += 3.0 * direction
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
+    tensors = [qkv.to(dtype), keys.to(dtype), values.to(dtype), table, q_start,
+               torch.tensor(pos0, dtype=torch.int32), torch.tensor(kv_lens, dtype=torch.int32)]
+    return tensors, kv_lens
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [
+    (12, 2, 128, 16, 0), (16, 1, 64, 32, 0), (3, 1, 32, 16, 0), (28, 4, 128, 16, 300), (8, 8, 64, 48, 0), (6, 2, 128, 64, 33),
+])
+def test_decode_attention_over_long_contexts(ops, heads, kv_heads, d, page, window):
+    """Single tokens over contexts from one key to thousands, cut into slices and merged."""
+    gen = torch.Generator().manual_seed(21)
+    kv = [4096, 777, 17, 1, 16, 2049, 65]
+    tensors, kv_lens = _paged_case(gen, [1] * len(kv), [n - 1 for n in kv], heads, kv_heads, d, page, torch.bfloat16)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=1,
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
+    want = ref.paged_attention(*tensors, **args)
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=len(kv))
+    _close(got, want, torch.bfloat16, scale=2.0)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [
+    (12, 2, 128, 16, 0), (4, 4, 64, 16, 0), (3, 1, 32, 32, 0), (6, 3, 128, 16, 100), (2, 1, 64, 64, 17),
+])
+def test_prefill_attention_portions_at_offsets(ops, heads, kv_heads, d, page, window):
+    """Portions of prompts at any offset (ragged against the 64-token blocks and the pages),
+    beside single tokens, in one launch."""
+    gen = torch.Generator().manual_seed(22)
+    q_lens = [300, 1, 65, 2, 64, 1, 129]
+    pos0 = [0, 500, 1000, 31, 64, 0, 77]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
+    want = ref.paged_attention(*tensors, **args)
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    _close(got, want, torch.bfloat16, scale=2.0)
+    got2 = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=2)
+    assert torch.equal(got, got2)
+
+
+def test_tensor_core_attention_agrees_with_the_cuda_core_kernel(ops):
+    gen = torch.Generator().manual_seed(23)
+    q_lens, pos0 = [1, 40, 1, 7], [99, 3, 0, 60]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, 6, 2, 64, 16, torch.bfloat16)
+    args = dict(num_heads=6, num_kv_heads=2, head_dim=64, page_size=16, max_q_len=40, max_kv_len=max(kv_lens),
+                scale=0.125, window=0)
+    fast = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    ops.use_tensor_cores = False
+    try:
+        slow = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    finally:
+        ops.use_tensor_cores = True
+    assert (fast.float() - slow.float()).abs().max().item() <= 2.0 ** -6 * float(slow.float().abs().max())
