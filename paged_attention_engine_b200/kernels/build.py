@@ -26,7 +26,7 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared",
 ]
 
 # family -> sources (the first is compiled, the others are headers it includes)
@@ -36,7 +36,7 @@ FAMILIES: dict[str, list[str]] = {
     "attention_simt": ["attention_simt.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
-    "attention_mma": ["attention_mma.cu", "common.cuh"],
+    "attention_mma": ["attention_mma.cu", "attention_mma.cuh", "common.cuh"],
 }
 
 _lock = threading.Lock()
@@ -107,6 +107,9 @@ def _compile(name: str, target: Path) -> None:
         partial.unlink(missing_ok=True)
         raise RuntimeError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(partial, target)
+    for stale in target.parent.glob(f"libpae_{name}_????????????.so"):
+        if stale != target:
+            stale.unlink(missing_ok=True)      # an older build of the same family
     say(f"built {target.name} in {time.time() - started:.0f} s")
 
 
