@@ -143,7 +143,6 @@ def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampler_cls,
     for pool in cache.pools:
         pool.normal_(0.0, 0.5)
     runner = engine.new_runner(cache)
-    sampler = sampler_cls(engine.runtime.ops, engine.device)
     keys = standing_requests(runner, cache, batch, start_context, engine.vocab_size, torch)
     gen = torch.Generator().manual_seed(batch)
     rows = [sampling_row(0.0, 0, i, 0) for i in range(batch)]
@@ -152,8 +151,7 @@ def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampler_cls,
     def one(i):
         for key in keys:
             assert cache.manager.reserve(key, 1).ok
-        out = runner.step([StepEntry(key, (tokens[i][b],), (0,)) for b, key in enumerate(keys)])
-        return sampler.sample(out.logits, rows)
+        return runner.step([StepEntry(key, (tokens[i][b],), (0,)) for b, key in enumerate(keys)], rows).tokens
 
     for i in range(warmup):
         one(i)
@@ -255,6 +253,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the configuration has (both numbers are reported)")
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    parser.add_argument("--only", choices=("all", "decode", "prefill"), default="all",
+                        help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -279,6 +279,18 @@ def main() -> int:
     model["num_hidden_layers"] = args.layers
     engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
     peak = peaks()
+
+    if args.only == "prefill":
+        prefill_ms = time_prefill(engine, torch)
+        flops = prefill_flops(model, PREFILL_TOKENS)
+        print(json.dumps({"only": "prefill", "ms": round(prefill_ms, 3), "tokens": PREFILL_TOKENS,
+                          "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)}))
+        return 0
+    if args.only == "decode":
+        decode = time_decode(engine, args.batch, args.steps, warmup, torch, Sampler, SamplingRow)
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(decode["ms_per_step"], 4),
+                          "tokens_per_s": round(decode["tokens_per_s"], 1), "launches": decode["launches"]}))
+        return 0
 
     sampler = ClockSampler()
     sampler.start()

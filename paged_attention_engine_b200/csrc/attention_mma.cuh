@@ -28,6 +28,8 @@
 #include "common.cuh"
 
 #include <cfloat>
+#include <mutex>
+#include <unordered_set>
 
 namespace pae_attention {
 
@@ -434,12 +436,17 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
   }
 }
 
+// Raises a kernel's dynamic shared memory limit, once per kernel and process.
 template <typename Kernel>
 int allow_smem(Kernel kernel, size_t bytes, const char* what) {
-  if (bytes > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (err != cudaSuccess) return fail(100, "%s: %s", what, cudaGetErrorString(err));
-  }
+  static std::mutex mutex;
+  static std::unordered_set<const void*> done;
+  if (bytes <= 48 * 1024) return 0;
+  std::lock_guard<std::mutex> guard(mutex);
+  if (done.count((const void*)kernel)) return 0;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (err != cudaSuccess) return fail(100, "%s: %s", what, cudaGetErrorString(err));
+  done.insert((const void*)kernel);
   return 0;
 }
 

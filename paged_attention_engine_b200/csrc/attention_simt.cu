@@ -147,9 +147,11 @@ int launch(void* out, const void* qkv, const void* keys, const void* values, con
            int d, int page_size, float scale, int window, cudaStream_t s) {
   const size_t bytes = smem_bytes(d);
   auto kernel = paged_attention_simt_kernel<T>;
-  if (bytes > 48 * 1024) {
-    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  static bool raised = false;   // per element type: the limit is raised once, to the most any head size needs
+  if (bytes > 48 * 1024 && !raised) {
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes(MAX_D));
     if (err != cudaSuccess) return fail(100, "paged_attention_simt: %s", cudaGetErrorString(err));
+    raised = true;
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, heads, seqs);
   kernel<<<grid, THREADS, bytes, s>>>((T*)out, (const T*)qkv, (const T*)keys, (const T*)values, block_table,

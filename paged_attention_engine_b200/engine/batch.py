@@ -61,6 +61,9 @@ class StepContext:
     host_q_lens: list[int] = field(default_factory=list)
     host_q_pos0: list[int] = field(default_factory=list)
     host_state_slots: list[int] = field(default_factory=list)
+    # (temperature, seed_lo, seed_hi, request_key, output_index), one element per wanted place
+    sampling: tuple | None = None
+    buffer: torch.Tensor | None = None    # the one device tensor that all integer arrays above are views of
     memo: dict = field(default_factory=dict)
 
 
@@ -75,9 +78,15 @@ class _Staging:
         self.events: list[Any] = [None] * turns
         self.turn = 0
 
-    def upload(self, flat: np.ndarray) -> torch.Tensor:
+    def upload(self, flat: np.ndarray, into: torch.Tensor | None = None) -> torch.Tensor:
+        """Copies `flat` to the device: into `into` (a buffer that kernels of a captured
+        graph read) when given, else into a fresh tensor."""
         if not self.pinned:
-            return torch.from_numpy(flat.copy())
+            fresh = torch.from_numpy(flat.copy())
+            if into is None:
+                return fresh
+            into[: flat.size].copy_(fresh)
+            return into
         i = self.turn
         self.turn = (self.turn + 1) % len(self.buffers)
         if self.events[i] is not None:
@@ -87,8 +96,8 @@ class _Staging:
             buf = torch.empty(max(flat.size, 4096), dtype=torch.int32).pin_memory()
             self.buffers[i] = buf
         buf[: flat.size].copy_(torch.from_numpy(flat))
-        out = torch.empty(flat.size, dtype=torch.int32, device=self.device)
-        out.copy_(buf[: flat.size], non_blocking=True)
+        out = into if into is not None else torch.empty(flat.size, dtype=torch.int32, device=self.device)
+        out[: flat.size].copy_(buf[: flat.size], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.events[i] = event
@@ -108,15 +117,32 @@ def _pack(sections: list[np.ndarray]) -> tuple[np.ndarray, list[tuple[int, int]]
     return flat, spans
 
 
+def _signed32(value: int) -> int:
+    value &= 0xFFFFFFFF
+    return value - (1 << 32) if value >= (1 << 31) else value
+
+
 class BatchBuilder:
-    def __init__(self, manager: CacheManager, ops: Any, dtype: torch.dtype, device) -> None:
+    def __init__(self, manager: CacheManager, ops: Any, dtype: torch.dtype, device, vocab_size: int | None = None) -> None:
         self.manager = manager
         self.ops = ops
         self.dtype = dtype
         self.device = torch.device(device)
+        self.vocab_size = vocab_size
         self.staging = _Staging(self.device)
+        self.bytes_uploaded = 0
 
-    def build(self, entries: Sequence[StepEntry]) -> StepContext:
+    def build(
+        self,
+        entries: Sequence[StepEntry],
+        sampling: Sequence[Any] | None = None,
+        table_width: int | None = None,
+        into: torch.Tensor | None = None,
+    ) -> StepContext:
+        """Flattens the entries. `sampling` (one row per wanted place: temperature, seed,
+        request key, output index) travels in the same copy. `table_width` fixes the width of
+        the block tables (a captured graph needs the same layout every step) and `into` is
+        the device buffer that such a graph reads."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         manager = self.manager
@@ -148,6 +174,9 @@ class BatchBuilder:
         np.cumsum(q_lens, out=q_start[1:])
         total = int(q_start[-1])
         token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        if self.vocab_size is not None and ((token_ids < 0) | (token_ids >= self.vocab_size)).any():
+            bad = int(token_ids[(token_ids < 0) | (token_ids >= self.vocab_size)][0])
+            raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
         seq_index = np.repeat(np.arange(b, dtype=np.int32), q_lens)
         positions = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
         kv_len = np.asarray(pos0, dtype=np.int32) + np.asarray(q_lens, dtype=np.int32)
@@ -160,6 +189,10 @@ class BatchBuilder:
         ]
         max_kv = int(kv_len.max())
         width = (max_kv + page - 1) // page
+        if table_width is not None:
+            if table_width < width:
+                raise ValueError(f"block tables of {width} pages do not fit the fixed width {table_width}")
+            width = table_width
         for g in range(len(manager.groups)):
             table = manager.table_rows(g, slots_of, width)
             page_of_token = table[seq_index, positions // page]
@@ -169,9 +202,21 @@ class BatchBuilder:
                     f"request {entries[int(seq_index[bad])].key!r}: position {int(positions[bad])} has no page in group {g}"
                 )
             sections += [np.ascontiguousarray(table), page_of_token * page + positions % page]
+        first_sampling = len(sections)
+        if sampling is not None:
+            if len(sampling) != len(rows):
+                raise ValueError(f"{len(sampling)} sampling rows for {len(rows)} wanted places")
+            sections += [
+                np.asarray([r.temperature for r in sampling], dtype=np.float32).view(np.int32),
+                np.asarray([_signed32(r.seed) for r in sampling], dtype=np.int32),
+                np.asarray([_signed32(r.seed >> 32) for r in sampling], dtype=np.int32),
+                np.asarray([_signed32(r.request_key) for r in sampling], dtype=np.int32),
+                np.asarray([_signed32(r.output_index) for r in sampling], dtype=np.int32),
+            ]
 
         flat, spans = _pack(sections)
-        dev = self.staging.upload(flat)
+        dev = self.staging.upload(flat, into)
+        self.bytes_uploaded = 4 * flat.size
 
         def part(i: int) -> torch.Tensor:
             start, size = spans[i]
@@ -180,10 +225,16 @@ class BatchBuilder:
         groups = []
         for g in range(len(manager.groups)):
             groups.append(GroupStep(part(8 + 2 * g).view(b, width), part(9 + 2 * g)))
+        sampling_parts = None
+        if sampling is not None:
+            f = first_sampling
+            sampling_parts = (part(f).view(torch.float32), part(f + 1), part(f + 2), part(f + 3), part(f + 4))
         return StepContext(
             ops=self.ops, dtype=self.dtype, device=self.device, num_tokens=total, num_seqs=b,
             token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
             kv_len=part(5), state_slot=part(6), logit_rows=part(7),
-            max_q_len=max(q_lens), max_kv_len=max_kv, num_single=sum(1 for n in q_lens if n == 1), groups=groups,
+            max_q_len=max(q_lens), max_kv_len=width * page if table_width is not None else max_kv,
+            num_single=sum(1 for n in q_lens if n == 1), groups=groups,
             host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
+            sampling=sampling_parts, buffer=dev,
         )

@@ -44,10 +44,10 @@ class ModelExecutor:
                 rows.append(
                     SamplingRow(request.temperature, request.seed or 0, request.sampling_key, len(w.seq.generated))
                 )
-        output = self.runner.step(entries)
+        output = self.runner.step(entries, rows if rows else None)
         results = [WorkResult(None) for _ in work]
         if rows:
-            tokens = self.sampler.sample(output.logits, rows).cpu().tolist()
+            tokens = output.tokens.cpu().tolist()
             logits = output.logits.float().cpu() if record_logits else None
             at = 0
             for i, w in enumerate(work):

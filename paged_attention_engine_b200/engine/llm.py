@@ -84,8 +84,8 @@ class Engine:
         manager = CacheManager(self.cache_plan.groups, num_blocks, block_size, max_num_seqs)
         return PagedKVCache(self.cache_plan, manager, self.dtype, self.device)
 
-    def new_runner(self, cache: PagedKVCache) -> ModelRunner:
-        return ModelRunner(self.model, cache)
+    def new_runner(self, cache: PagedKVCache, use_graphs: bool = True) -> ModelRunner:
+        return ModelRunner(self.model, cache, use_graphs)
 
     @property
     def vocab_size(self) -> int:

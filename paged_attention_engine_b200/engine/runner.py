@@ -6,12 +6,18 @@ steps left, whatever the mix: portions of prompts beside single decoded tokens, 
 anywhere. Room for the tokens must have been reserved before (capacity is the
 caller's decision, as in engine/scheduler.py:255-266 and engine/model.py:386-397);
 the step never allocates pages.
+
+A step that only decodes (every entry brings one token and wants its logits) is
+launch-bound: some hundreds of small kernels. Such a step is captured once per (batch
+size, block-table width) into a CUDA graph whose kernels read the step's integers from a
+fixed device buffer, and replayed afterwards. The graph holds the same kernels as the
+eager step; what it computes does not differ.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Hashable, Sequence
+from typing import Any, Hashable, Sequence
 
 import torch
 
@@ -22,21 +28,40 @@ from .model import DecoderModel
 
 @dataclass
 class StepOutput:
-    """`logits[i]` belongs to `wanted[i]` = (request key, offset among the entry's tokens)."""
+    """`logits[i]` belongs to `wanted[i]` = (request key, offset among the entry's tokens);
+    `tokens[i]` is the token sampled from it when sampling rows were given. Both live on the
+    device and are valid until the next step."""
 
     logits: torch.Tensor | None
     wanted: list[tuple[Hashable, int]]
     num_tokens: int
+    tokens: torch.Tensor | None = None
+
+
+class _DecodeGraph:
+    def __init__(self, buffer: torch.Tensor) -> None:
+        self.buffer = buffer
+        self.graph: Any = None
+        self.logits: torch.Tensor | None = None
+        self.tokens: torch.Tensor | None = None
+        self.launches = 0
 
 
 class ModelRunner:
-    def __init__(self, model: DecoderModel, cache: PagedKVCache) -> None:
+    MAX_GRAPHS = 24
+
+    def __init__(self, model: DecoderModel, cache: PagedKVCache, use_graphs: bool = True) -> None:
         self.model = model
         self.cache = cache
         self.manager = cache.manager
         self.runtime = model.runtime
-        self.builder = BatchBuilder(self.manager, self.runtime.ops, self.runtime.dtype, self.runtime.device)
+        self.builder = BatchBuilder(
+            self.manager, self.runtime.ops, self.runtime.dtype, self.runtime.device, model.spec.vocab_size
+        )
         self.entry_caches = [cache.entry_cache(p) for p in range(len(model.spec.schedule))]
+        self.use_graphs = use_graphs and self.runtime.device.type == "cuda"
+        self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self.graph_replays = 0
 
     def begin_request(self, key: Hashable) -> bool:
         """Registers a request (state slot, empty block tables); False when no slot is free."""
@@ -49,11 +74,71 @@ class ModelRunner:
     def end_request(self, key: Hashable) -> int:
         return self.manager.free_request(key)
 
-    @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> StepOutput:
-        ctx = self.builder.build(entries)
+    # ------------------------------------------------------------------ #
+
+    def _run(self, ctx):
         logits = self.model.forward(ctx, self.entry_caches)
+        tokens = None
+        if ctx.sampling is not None and logits is not None:
+            tokens = self.runtime.ops.sample(logits, *ctx.sampling)
+        return logits, tokens
+
+    def _graph_key(self, entries, sampling) -> tuple[int, int, bool] | None:
+        if not self.use_graphs or len(entries) > 256:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or tuple(e.want) != (0,):
+                return None
+        page = self.manager.block_size
+        longest = max(self.manager.num_computed(e.key) + 1 for e in entries)
+        width = 16
+        while width * page < longest:
+            width *= 2
+        return (len(entries), width, sampling is not None)
+
+    @torch.inference_mode()
+    def step(self, entries: Sequence[StepEntry], sampling: Sequence[Any] | None = None) -> StepOutput:
+        key = self._graph_key(entries, sampling)
+        slot = self.graphs.get(key) if key is not None else None
+        if slot is not None and slot.graph is not None:
+            self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer)
+            slot.graph.replay()
+            self.model.forward_pass_count += 1
+            self.graph_replays += 1
+            ops = self.runtime.ops
+            if hasattr(ops, "launches"):
+                ops.launches += slot.launches
+            logits, tokens = slot.logits, slot.tokens
+            num_tokens = len(entries)
+        elif key is not None and len(self.graphs) < self.MAX_GRAPHS:
+            # First time for this shape: run it eagerly out of the buffer the graph will read
+            # (that is this step's real work), then record the same launches without running them.
+            ctx = self.builder.build(entries, sampling, table_width=key[1])
+            slot = _DecodeGraph(ctx.buffer)
+            self.graphs[key] = slot
+            logits, tokens = self._run(ctx)
+            num_tokens = ctx.num_tokens
+            self._capture(slot, entries, sampling, key)
+        else:
+            ctx = self.builder.build(entries, sampling)
+            logits, tokens = self._run(ctx)
+            num_tokens = ctx.num_tokens
         for e in entries:
             self.manager.advance(e.key, len(e.tokens))
         wanted = [(e.key, int(w)) for e in entries for w in e.want]
-        return StepOutput(logits, wanted, ctx.num_tokens)
+        return StepOutput(logits, wanted, num_tokens, tokens)
+
+    def _capture(self, slot: _DecodeGraph, entries, sampling, key) -> None:
+        ops = self.runtime.ops
+        torch.cuda.synchronize()
+        ctx = self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer)
+        before = getattr(ops, "launches", 0)
+        graph = torch.cuda.CUDAGraph()
+        count = self.model.forward_pass_count
+        with torch.cuda.graph(graph):
+            slot.logits, slot.tokens = self._run(ctx)
+        self.model.forward_pass_count = count       # recording is not a traversal
+        slot.launches = getattr(ops, "launches", 0) - before
+        if hasattr(ops, "launches"):
+            ops.launches = before
+        slot.graph = graph

@@ -1,0 +1,114 @@
+"""Generation through the entry point on the GPU: greedy tokens against the plain
+implementation, decode steps through captured graphs against eager steps, long decoding,
+the first tokens of a sequence, preemption and recompute under a tiny pool."""
+
+import pytest
+import torch
+
+import helpers
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _folder(tmp_path_factory, name, dtype_name, sharpen=4.0):
+    raw, page, seed = helpers.TINY[name]
+    folder = helpers.write_model(tmp_path_factory.mktemp(f"{name}_{dtype_name}"), raw, seed, DTYPES[dtype_name], sharpen=sharpen)
+    return folder, raw, page
+
+
+def _teacher_forced_check(folder, dtype, prompt, tokens, step_logits):
+    """Greedy tokens may differ between precisions where two logits nearly tie; what must hold is
+    that every step's logits are those of the plain model for the engine's own token history."""
+    oracle = helpers.plain_logits(folder, list(prompt) + list(tokens))[len(prompt) - 1 : -1]
+    got = torch.stack(step_logits)
+    gap = (got - oracle).abs().max().item()
+    assert gap <= helpers.tolerance(dtype, oracle), f"max |dlogit| {gap}"
+    margin = 2 * helpers.tolerance(dtype, oracle)
+    for row, token in zip(oracle, tokens):
+        assert row[token].item() >= row.max().item() - margin, "the sampled token is not the plain model's best"
+
+
+@pytest.mark.parametrize("name", list(helpers.TINY))
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_greedy_generation_through_the_entry_point(tmp_path_factory, name, dtype_name):
+    from paged_attention_engine_b200 import LLM, Request
+
+    folder, raw, page = _folder(tmp_path_factory, name, dtype_name)
+    llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=64, block_size=page, max_num_seqs=4,
+                              max_num_batched_tokens=24, record_logits=True)
+    prompts = {f"p{i}": tuple(helpers.random_tokens(raw["vocab_size"], n, 300 + n)) for i, n in enumerate((5, 11, 17, 1, 30))}
+    for rid, prompt in prompts.items():
+        assert llm.add_request(Request(rid, prompt, 8))
+    out = llm.run_to_completion()
+    cfg, weights = plain.read_config(folder), {k: v.float() for k, v in plain.read_weights(folder).items()}
+    for rid, prompt in prompts.items():
+        assert len(out[rid]) == 8
+        _teacher_forced_check(folder, DTYPES[dtype_name], prompt, out[rid], llm.scheduler.finished[rid].step_logits)
+        if dtype_name == "float32":
+            want, _ = plain.generate_greedy(list(prompt), 8, weights, cfg)
+            assert list(out[rid]) == want
+    assert llm.runner.graph_replays > 0, "decode steps are expected to run as captured graphs"
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_graph_steps_equal_eager_steps(tmp_path_factory, dtype_name):
+    """The captured graph holds the same launches as the eager step: the logits are the same bits."""
+    from paged_attention_engine_b200 import LLM, Request
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_b", dtype_name)
+    prompts = {f"g{i}": tuple(helpers.random_tokens(raw["vocab_size"], n, 400 + n)) for i, n in enumerate((9, 16, 33))}
+
+    def run(use_graphs):
+        llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=64, block_size=page, record_logits=True,
+                                  use_graphs=use_graphs)
+        for rid, prompt in prompts.items():
+            llm.add_request(Request(rid, prompt, 20, temperature=0.7, seed=11))
+        out = llm.run_to_completion()
+        return out, {rid: torch.stack(llm.scheduler.finished[rid].step_logits) for rid in prompts}, llm.runner.graph_replays
+
+    out_g, logits_g, replays = run(True)
+    out_e, logits_e, none = run(False)
+    assert replays > 10 and none == 0
+    assert out_g == out_e
+    for rid in prompts:
+        assert torch.equal(logits_g[rid], logits_e[rid])
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_long_decoding_and_first_tokens(tmp_path_factory, dtype_name):
+    """A one-token prompt decoded far past several page edges and graph widths: the first
+    tokens of a sequence, and every later one, against the plain model."""
+    from paged_attention_engine_b200 import LLM, Request
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_c", dtype_name, sharpen=3.0)
+    llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=80, block_size=page, record_logits=True)
+    prompt = (7,)
+    llm.add_request(Request("long", prompt, 300))
+    out = llm.run_to_completion()
+    assert len(out["long"]) == 300
+    _teacher_forced_check(folder, DTYPES[dtype_name], prompt, out["long"], llm.scheduler.finished["long"].step_logits)
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_preemption_and_recompute_on_the_gpu(tmp_path_factory, dtype_name):
+    from paged_attention_engine_b200 import LLM, EventKind, Request
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_b", dtype_name)
+    prompts = {f"s{i}": tuple(helpers.random_tokens(raw["vocab_size"], n, 500 + n)) for i, n in enumerate((20, 31, 12, 40))}
+
+    def run(num_blocks):
+        llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=num_blocks, block_size=page, record_logits=True)
+        for rid, prompt in prompts.items():
+            assert llm.add_request(Request(rid, prompt, 24))
+        return llm.run_to_completion(), llm
+
+    roomy, _ = run(64)
+    tight, llm = run(7)          # 112 token slots for four requests that grow to 44..64 tokens each
+    assert llm.scheduler.events_of(EventKind.PREEMPT)
+    for rid, prompt in prompts.items():
+        _teacher_forced_check(folder, DTYPES[dtype_name], prompt, tight[rid], llm.scheduler.finished[rid].step_logits)
+    if dtype_name == "float32":
+        assert tight == roomy
