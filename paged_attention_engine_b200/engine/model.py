@@ -48,6 +48,10 @@ class DecoderModel:
                 )
             )
         self.forward_pass_count = 0
+        parts = [self.embedding, self.head, self.final_norm]
+        for layer in self.layers:
+            parts += [layer.block, layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward]
+        self.graph_safe = all(getattr(part, "graph_safe", True) for part in parts)
 
     def forward(self, ctx, entry_caches) -> torch.Tensor | None:
         """Runs the step's tokens through every schedule entry; float32 logits

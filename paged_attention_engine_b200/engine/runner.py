@@ -59,7 +59,7 @@ class ModelRunner:
             self.manager, self.runtime.ops, self.runtime.dtype, self.runtime.device, model.spec.vocab_size
         )
         self.entry_caches = [cache.entry_cache(p) for p in range(len(model.spec.schedule))]
-        self.use_graphs = use_graphs and self.runtime.device.type == "cuda"
+        self.use_graphs = use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
         self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self.graph_replays = 0
 

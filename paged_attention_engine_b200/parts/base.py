@@ -24,6 +24,8 @@ What each kind of part must provide:
                 `cache` is the `EntryCache` of the schedule entry that runs.
   feed-forward  `forward(ctx, x, residual) -> residual + ff(x)`.
   block         `forward(ctx, hidden, layer, cache) -> hidden`.
+
+A part whose forward() looks at the step's host-side fields declares `graph_safe = False`.
 """
 
 from __future__ import annotations
@@ -91,6 +93,13 @@ class Runtime:
 
 
 class Part:
+    # A step that only decodes is recorded once as a CUDA graph and replayed. That is sound
+    # for a part whose forward() depends on the step only through device tensors of `ctx`
+    # (and its batch size). A part that reads the step's host-side fields (`host_q_lens`,
+    # `host_state_slots`, ...) or branches on values sets this to False; a model that holds
+    # such a part always runs eagerly.
+    graph_safe = True
+
     @classmethod
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
         return []

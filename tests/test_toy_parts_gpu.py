@@ -1,0 +1,147 @@
+"""The assembly is general: with parts defined HERE, in the test, and registered under new
+names, a model is built, given pages and state by the cache manager, and stepped, without
+a change to any file of the package.
+
+  * `running_mean` is a mixer with state of its own and no keys or values: it adds to every
+    token the mean of all tokens of its request so far. Its state (a sum and a count per
+    request) lives in the cache manager's state slots, is zero for a new request, carries
+    over portions and steps, and belongs to one request only.
+  * the schedule names a layer twice (shared weights, a cache per run), and lets an entry
+    read the keys and values that an earlier entry wrote.
+
+These are toys for the test, not models of anything.
+"""
+
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def _register_toys():
+    from paged_attention_engine_b200.parts import MIXERS, Part, StateNeed
+
+    if "running_mean" in MIXERS.names():
+        return
+
+    @MIXERS.register("running_mean")
+    class RunningMean(Part):
+        """params: hidden_size. No tensors, no pages; state [hidden + 1] per request."""
+
+        graph_safe = False      # forward() loops over the step's requests on the host
+
+        @classmethod
+        def state_need(cls, spec):
+            return StateNeed((int(spec.params["hidden_size"]) + 1,), torch.float32)
+
+        def forward(self, ctx, x, residual, cache):
+            out = residual.clone()
+            at = 0
+            for slot, count in zip(ctx.host_state_slots, ctx.host_q_lens):
+                state = cache.state[slot]
+                rows = x[at : at + count].float()
+                sums = state[:-1] + rows.cumsum(0)
+                counts = state[-1] + torch.arange(1, count + 1, device=x.device, dtype=torch.float32)
+                out[at : at + count] += (sums / counts[:, None]).to(out.dtype)
+                state[:-1] = sums[-1]
+                state[-1] = counts[-1]
+                at += count
+            return out
+
+
+def _spec(hidden, vocab, schedule_kind):
+    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    def norm(prefix):
+        return PartSpec("rms_norm", {"size": hidden, "eps": 1e-5}, prefix)
+
+    attention = PartSpec("gqa_attention", {
+        "hidden_size": hidden, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qkv_bias": True, "scale": 0.25,
+        "window": 0, "position_encoding": {"kind": "rotary", "head_dim": 16, "theta": 1e4}}, "l0.attn")
+    layers = (
+        LayerSpec("pre_norm_residual", norm("l0.n1"), attention, norm("l0.n2"),
+                  PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48}, "l0.ff")),
+        LayerSpec("pre_norm_residual", norm("l1.n1"), PartSpec("running_mean", {"hidden_size": hidden}), norm("l1.n2"),
+                  PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 40}, "l1.ff")),
+    )
+    schedule = {
+        "stateful": (ScheduleEntry(0), ScheduleEntry(1)),
+        "twice": (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)),
+        "shared_cache": (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0, cache_from=0)),
+    }[schedule_kind]
+    return ModelSpec("toy", vocab, hidden, 256, PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden}, "emb"),
+                     layers, schedule, norm("final"), PartSpec("lm_head", {"vocab_size": vocab, "hidden_size": hidden, "tied_to": "emb.weight"}, "head"))
+
+
+def _plain_forward(spec, w, ids):
+    """The same toy model written out whole-sequence with the plain implementation's functions."""
+    from plain import qwen2_plain as plain
+
+    x = w["emb.weight"][torch.tensor(ids)]
+    n = len(ids)
+    cos, sin = plain.rotary_tables(plain.rotary_inv_freq(16, 1e4), torch.arange(n), torch.float32)
+    cfg = plain.PlainConfig(2, x.shape[1], 4, 2, 16, 48, w["emb.weight"].shape[0], 1e-5, 1e4, True, (0, 0))
+    kv_of_entry = {}
+    for position, entry in enumerate(spec.schedule):
+        p = f"l{entry.layer}."
+        normed = plain.rms_norm(x, w[p + "n1.weight"], 1e-5)
+        if entry.layer == 0:
+            source = normed if entry.cache_from is None else kv_of_entry[entry.cache_from]
+            kv_of_entry[position] = normed
+            q = plain.apply_rotary(plain.linear(normed, w[p + "attn.q_proj.weight"], w[p + "attn.q_proj.bias"]).view(n, 4, 16), cos, sin)
+            k = plain.apply_rotary(plain.linear(source, w[p + "attn.k_proj.weight"], w[p + "attn.k_proj.bias"]).view(n, 2, 16), cos, sin)
+            v = plain.linear(source, w[p + "attn.v_proj.weight"], w[p + "attn.v_proj.bias"]).view(n, 2, 16)
+            x = x + plain.linear(plain.attention(q, k, v, 0.25).reshape(n, 64), w[p + "attn.o_proj.weight"])
+        else:
+            x = x + normed.cumsum(0) / torch.arange(1, n + 1)[:, None]
+        normed = plain.rms_norm(x, w[p + "n2.weight"], 1e-5)
+        x = x + plain.swiglu(normed, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["emb.weight"])
+
+
+@pytest.mark.parametrize("schedule_kind", ["stateful", "twice", "shared_cache"])
+def test_toy_model_is_registered_built_and_stepped(schedule_kind):
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.kernels import ops
+    from paged_attention_engine_b200.parts import Runtime
+    from paged_attention_engine_b200.weights import collect_tensor_specs, place_tensors
+    from paged_attention_engine_b200.weights.random_init import draw
+
+    _register_toys()
+    hidden, vocab = 64, 97
+    spec = _spec(hidden, vocab, schedule_kind)
+    gen = torch.Generator().manual_seed(9)
+    raw = {name: draw(t, gen) * (5.0 if ".q_proj." in name or ".k_proj." in name else 1.0)
+           for name, t in sorted(collect_tensor_specs(spec).items())}
+    runtime = Runtime(ops, torch.float32, torch.device("cuda:0"))
+    engine = Engine(None, spec, place_tensors(dict(raw), spec, torch.float32, runtime.device), runtime)
+
+    plan = engine.cache_plan
+    assert len(plan.state_needs) == sum(1 for e in spec.schedule if e.layer == 1)
+    owners = [pos for pos, e in enumerate(spec.schedule) if e.layer == 0 and e.cache_from is None]
+    assert plan.groups[0].entries == tuple(owners)
+
+    cache = engine.new_paged_cache(num_blocks=24, block_size=8, max_num_seqs=3)
+    runner = engine.new_runner(cache)
+    requests = {"a": helpers.random_tokens(vocab, 41, 1), "b": helpers.random_tokens(vocab, 23, 2), "c": helpers.random_tokens(vocab, 30, 3)}
+    trace = helpers.trace_mixed(requests, seed=4, live_limit=2, decode_tail=6)
+    outputs = {}
+    for record in trace:
+        entries = []
+        for item in record["entries"]:
+            if not cache.manager.is_live(item["id"]):
+                assert runner.begin_request(item["id"])
+            assert cache.manager.reserve(item["id"], len(item["tokens"])).ok
+            entries.append(StepEntry(item["id"], item["tokens"], item["want"]))
+        outputs[record["step"]] = runner.step(entries).logits.float().cpu()
+        for key in record["end"]:
+            runner.end_request(key)
+    got = helpers.collect(trace, outputs, requests)
+    for key, ids in requests.items():
+        want = _plain_forward(spec, raw, ids)
+        gap = (got[key] - want).abs().max().item()
+        assert gap <= helpers.tolerance(torch.float32, want), f"{schedule_kind}/{key}: {gap}"
+    assert cache.manager.slots.num_free == 3 and cache.manager.allocators[0].num_free == 24
