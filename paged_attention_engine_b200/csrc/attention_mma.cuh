@@ -215,6 +215,7 @@ struct DecodeParams {
 
 template <int D>
 __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const DecodeParams p) {
+  dependent_launch_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x * DECODE_WARPS + warp;
@@ -297,11 +298,17 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const 
 }
 
 // out[token, head, :] = sum_s w_s part_out[s] / sum_s w_s part_sum[s], w_s = 2^(max_s - max).
+// One block per (request, head): the weights of all slices are worked out once, in parallel,
+// into shared memory; then every thread owns one output dimension and folds the slices in
+// their order with independent loads.
 template <int D>
 __global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_out,
                                     const float* __restrict__ part_max, const float* __restrict__ part_sum,
                                     const int* __restrict__ q_start, const int* __restrict__ kv_len, int heads, int window,
                                     int slice_keys, int max_slices) {
+  dependent_launch_prologue();
+  extern __shared__ float weights[];          // [max_slices]
+  __shared__ float reduce[32];
   const int h = blockIdx.x, b = blockIdx.y;
   const int token = q_start[b];
   if (q_start[b + 1] - token != 1) return;
@@ -310,14 +317,39 @@ __global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float
   const int base = (first_key / TILE_KEYS) * TILE_KEYS;
   const int slices = min(max_slices, (n_kv - base + slice_keys - 1) / slice_keys);
   const size_t at = ((size_t)b * heads + h) * max_slices;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+
   float top = -FLT_MAX;
-  for (int s = 0; s < slices; ++s) top = fmaxf(top, part_max[at + s]);
+  for (int s = threadIdx.x; s < slices; s += blockDim.x) {
+    const float m = part_max[at + s];
+    weights[s] = m;
+    top = fmaxf(top, m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+  if (lane == 0) reduce[warp] = top;
+  __syncthreads();
+  top = reduce[0];
+  for (int w = 1; w < warps; ++w) top = fmaxf(top, reduce[w]);
+  __syncthreads();
+
   float total = 0.f;
-  for (int s = 0; s < slices; ++s) total += part_sum[at + s] * exp2f(part_max[at + s] - top);
+  for (int s = threadIdx.x; s < slices; s += blockDim.x) {
+    const float w = exp2f(weights[s] - top);
+    weights[s] = w;
+    total += part_sum[at + s] * w;
+  }
+  total = warp_sum(total);
+  if (lane == 0) reduce[warp] = total;
+  __syncthreads();
+  total = 0.f;
+  for (int w = 0; w < warps; ++w) total += reduce[w];
   const float inv = total > 0.f ? 1.f / total : 0.f;
+
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = 0.f;
-    for (int s = 0; s < slices; ++s) v += part_out[(at + s) * D + d] * exp2f(part_max[at + s] - top);
+#pragma unroll 8
+    for (int s = 0; s < slices; ++s) v += part_out[(at + s) * D + d] * weights[s];
     out[((size_t)token * heads + h) * D + d] = __float2bfloat16_rn(v * inv);
   }
 }
@@ -341,6 +373,7 @@ struct PrefillParams {
 
 template <int D>
 __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
+  dependent_launch_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -455,9 +488,10 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int seqs, cudaStrea
   const size_t bytes = (size_t)DECODE_WARPS * 4 * TILE_KEYS * D * 2;
   if (int err = allow_smem(decode_slices_kernel<D>, bytes, "paged_attention_decode")) return err;
   dim3 grid((p.max_slices + DECODE_WARPS - 1) / DECODE_WARPS, p.kv_heads, seqs);
-  decode_slices_kernel<D><<<grid, DECODE_WARPS * 32, bytes, s>>>(p);
+  launch_kernel(decode_slices_kernel<D>, grid, DECODE_WARPS * 32, bytes, s, p);
   if (int err = check_launch("paged_attention_decode")) return err;
-  merge_slices_kernel<D><<<dim3(p.heads, seqs), D >= 128 ? 128 : 64, 0, s>>>(out, p.part_out, p.part_max, p.part_sum, p.q_start,
+  if ((size_t)p.max_slices * sizeof(float) > 40 * 1024) return fail(2, "paged_attention_decode: %d slices are more than the merge takes", p.max_slices);
+  launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), D >= 128 ? 128 : 64, p.max_slices * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
                                                                      p.kv_len, p.heads, p.window, p.slice_keys, p.max_slices);
   return check_launch("paged_attention_merge");
 }
@@ -467,7 +501,7 @@ int launch_prefill(const PrefillParams& p, int seqs, int max_q_len, cudaStream_t
   const size_t bytes = (size_t)2 * 2 * PREFILL_BKEYS * D * 2;
   if (int err = allow_smem(prefill_kernel<D>, bytes, "paged_attention_prefill")) return err;
   dim3 grid((max_q_len + PREFILL_BQ - 1) / PREFILL_BQ, p.heads, seqs);
-  prefill_kernel<D><<<grid, 128, bytes, s>>>(p);
+  launch_kernel(prefill_kernel<D>, grid, 128, bytes, s, p);
   return check_launch("paged_attention_prefill");
 }
 

@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_simt_kernel(
     const int* __restrict__ block_table, int table_width, const int* __restrict__ q_start,
     const int* __restrict__ q_pos0, const int* __restrict__ kv_len, int heads, int kv_heads, int d, int page_size,
     float scale, int window) {
+  dependent_launch_prologue();
   extern __shared__ float smem[];
   const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
   const int first_token = q_start[b];
@@ -154,7 +155,7 @@ int launch(void* out, const void* qkv, const void* keys, const void* values, con
     raised = true;
   }
   dim3 grid((max_q_len + BQ - 1) / BQ, heads, seqs);
-  kernel<<<grid, THREADS, bytes, s>>>((T*)out, (const T*)qkv, (const T*)keys, (const T*)values, block_table,
+  launch_kernel(kernel, grid, THREADS, bytes, s, (T*)out, (const T*)qkv, (const T*)keys, (const T*)values, block_table,
                                       table_width, q_start, q_pos0, kv_len, heads, kv_heads, d, page_size, scale, window);
   return check_launch("paged_attention_simt");
 }

@@ -13,6 +13,8 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
+#include <utility>
 
 namespace pae {
 
@@ -55,6 +57,45 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// Programmatic dependent launch. Every kernel of these libraries starts with
+// `dependent_launch_prologue()` (for the tensor-core product: after its set-up that touches no
+// global memory) and is launched with `launch_kernel`, which marks it as allowed to start
+// while the kernel before it in the stream is still finishing. The prologue first lets the
+// NEXT kernel begin to launch, then waits until the kernel BEFORE has completed and its
+// writes are visible; nothing of global memory is read or written before that wait. So the
+// order of all memory effects is that of a plain stream, and only launch latencies and
+// prologues overlap. A step of decoding is several hundred small kernels; this is worth
+// about a third of its time. PAE_PDL=0 in the environment turns it off.
+__device__ __forceinline__ void dependent_launch_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void dependent_launch_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void dependent_launch_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool dependent_launch_enabled() {
+  static const bool enabled = [] {
+    const char* v = std::getenv("PAE_PDL");
+    return v == nullptr || std::atoi(v) != 0;
+  }();
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&config, kernel, KArgs(std::forward<Args>(args))...);   // errors surface in check_launch
 }
 
 }  // namespace pae

@@ -15,6 +15,7 @@ using namespace pae;
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ table,
                                    const int* __restrict__ index, int rows, int width) {
+  dependent_launch_prologue();
   const int r = blockIdx.x;
   const int src = index[r];
   const bool ok = src >= 0 && src < rows;
@@ -29,9 +30,9 @@ PAE_EXPORT int pae_gather_rows(void* out, const void* table, const int* index, i
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    gather_rows_kernel<float><<<n, threads, 0, s>>>((float*)out, (const float*)table, index, rows, width);
+    launch_kernel(gather_rows_kernel<float>, n, threads, 0, s, (float*)out, (const float*)table, index, rows, width);
   else if (dtype == kBF16)
-    gather_rows_kernel<__nv_bfloat16><<<n, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, index, rows, width);
+    launch_kernel(gather_rows_kernel<__nv_bfloat16>, n, threads, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, index, rows, width);
   else
     return fail(1, "gather_rows: unknown dtype %d", dtype);
   return check_launch("gather_rows");
@@ -45,6 +46,7 @@ PAE_EXPORT int pae_gather_rows(void* out, const void* table, const int* index, i
 template <typename T>
 __global__ void rms_norm_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ weight,
                                 int width, float eps) {
+  dependent_launch_prologue();
   __shared__ float partial[32];
   const T* row = x + (size_t)blockIdx.x * width;
   float sum = 0.f;
@@ -67,15 +69,83 @@ __global__ void rms_norm_kernel(T* __restrict__ out, const T* __restrict__ x, co
   for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = from_float<T>(to_float(row[i]) * scale * weight[i]);
 }
 
+// The same for bfloat16 rows whose width is a multiple of 8: 16-byte loads and stores, the
+// row kept in registers between the two passes. The sum runs over the same elements in
+// another order than the scalar kernel's; the order depends on the width only.
+template <int PER_THREAD>
+__global__ void rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x,
+                                       const float* __restrict__ weight, int width, float eps) {
+  dependent_launch_prologue();
+  __shared__ float partial[32];
+  const int chunks = width >> 3;
+  const uint4* row = (const uint4*)(x + (size_t)blockIdx.x * width);
+  uint4 held[PER_THREAD];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_THREAD; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < chunks) {
+      held[j] = row[c];
+      const __nv_bfloat162* h = (const __nv_bfloat162*)&held[j];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h[e]);
+        sum += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+  sum = warp_sum(sum);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) partial[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < warps ? partial[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) partial[0] = rsqrtf(v / (float)width + eps);
+  }
+  __syncthreads();
+  const float scale = partial[0];
+  uint4* to = (uint4*)(out + (size_t)blockIdx.x * width);
+#pragma unroll
+  for (int j = 0; j < PER_THREAD; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < chunks) {
+      const __nv_bfloat162* h = (const __nv_bfloat162*)&held[j];
+      const float4 w0 = *(const float4*)(weight + c * 8), w1 = *(const float4*)(weight + c * 8 + 4);
+      uint4 packed;
+      __nv_bfloat162* o = (__nv_bfloat162*)&packed;
+      float2 f;
+      f = __bfloat1622float2(h[0]); o[0] = __floats2bfloat162_rn(f.x * scale * w0.x, f.y * scale * w0.y);
+      f = __bfloat1622float2(h[1]); o[1] = __floats2bfloat162_rn(f.x * scale * w0.z, f.y * scale * w0.w);
+      f = __bfloat1622float2(h[2]); o[2] = __floats2bfloat162_rn(f.x * scale * w1.x, f.y * scale * w1.y);
+      f = __bfloat1622float2(h[3]); o[3] = __floats2bfloat162_rn(f.x * scale * w1.z, f.y * scale * w1.w);
+      to[c] = packed;
+    }
+  }
+}
+
 PAE_EXPORT int pae_rms_norm(void* out, const void* x, const float* weight, int rows, int width, float eps,
                             int dtype, void* stream) {
   if (rows == 0) return 0;
+  if (dtype == kBF16 && width % 8 == 0 && width <= 8 * 4 * 256 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0 &&
+      ((uintptr_t)weight & 15) == 0) {
+    const int chunks = width / 8;
+    const int block = chunks >= 256 ? 256 : ((chunks + 31) / 32) * 32;
+    const int per_thread = (chunks + block - 1) / block;
+    cudaStream_t vs = (cudaStream_t)stream;
+    auto* o = (__nv_bfloat16*)out;
+    auto* in = (const __nv_bfloat16*)x;
+    if (per_thread == 1) launch_kernel(rms_norm_bf16x8_kernel<1>, rows, block, 0, vs, o, in, weight, width, eps);
+    else if (per_thread == 2) launch_kernel(rms_norm_bf16x8_kernel<2>, rows, block, 0, vs, o, in, weight, width, eps);
+    else launch_kernel(rms_norm_bf16x8_kernel<4>, rows, block, 0, vs, o, in, weight, width, eps);
+    return check_launch("rms_norm");
+  }
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : (width >= 128 ? 128 : 32));
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    rms_norm_kernel<float><<<rows, threads, 0, s>>>((float*)out, (const float*)x, weight, width, eps);
+    launch_kernel(rms_norm_kernel<float>, rows, threads, 0, s, (float*)out, (const float*)x, weight, width, eps);
   else if (dtype == kBF16)
-    rms_norm_kernel<__nv_bfloat16><<<rows, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, weight, width, eps);
+    launch_kernel(rms_norm_kernel<__nv_bfloat16>, rows, threads, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, weight, width, eps);
   else
     return fail(1, "rms_norm: unknown dtype %d", dtype);
   return check_launch("rms_norm");
@@ -87,6 +157,7 @@ PAE_EXPORT int pae_rms_norm(void* out, const void* x, const float* weight, int r
 // ------------------------------------------------------------------------------------
 __global__ void rotary_table_kernel(float* __restrict__ table, const int* __restrict__ positions,
                                     const float* __restrict__ inv_freq, int tokens, int half) {
+  dependent_launch_prologue();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= tokens * half) return;
   const int t = i / half, f = i - t * half;
@@ -101,7 +172,7 @@ PAE_EXPORT int pae_rotary_table(float* table, const int* positions, const float*
                                 void* stream) {
   const long long n = (long long)tokens * half;
   if (n == 0) return 0;
-  rotary_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(table, positions, inv_freq, tokens, half);
+  launch_kernel(rotary_table_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, table, positions, inv_freq, tokens, half);
   return check_launch("rotary_table");
 }
 
@@ -118,6 +189,7 @@ __global__ void rotary_qk_cache_write_kernel(T* __restrict__ qkv, const float* _
                                              const int* __restrict__ slots, T* __restrict__ keys,
                                              T* __restrict__ values, int tokens, int heads, int kv_heads, int d,
                                              int page_size) {
+  dependent_launch_prologue();
   const int half = d >> 1;
   const int per_token = (heads + 2 * kv_heads) * half;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -157,9 +229,9 @@ PAE_EXPORT int pae_rotary_qk_cache_write(void* qkv, const float* table, const in
   const unsigned blocks = (unsigned)((n + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    rotary_qk_cache_write_kernel<float><<<blocks, 256, 0, s>>>((float*)qkv, table, slots, (float*)keys, (float*)values, tokens, heads, kv_heads, d, page_size);
+    launch_kernel(rotary_qk_cache_write_kernel<float>, blocks, 256, 0, s, (float*)qkv, table, slots, (float*)keys, (float*)values, tokens, heads, kv_heads, d, page_size);
   else if (dtype == kBF16)
-    rotary_qk_cache_write_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)qkv, table, slots, (__nv_bfloat16*)keys, (__nv_bfloat16*)values, tokens, heads, kv_heads, d, page_size);
+    launch_kernel(rotary_qk_cache_write_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)qkv, table, slots, (__nv_bfloat16*)keys, (__nv_bfloat16*)values, tokens, heads, kv_heads, d, page_size);
   else
     return fail(1, "rotary_qk_cache_write: unknown dtype %d", dtype);
   return check_launch("rotary_qk_cache_write");
@@ -171,6 +243,7 @@ PAE_EXPORT int pae_rotary_qk_cache_write(void* qkv, const float* table, const in
 // ------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, long long total, int inter) {
+  dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / inter;
@@ -180,15 +253,44 @@ __global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_
   out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
+// bfloat16 rows whose half-width is a multiple of 8: eight columns per thread, 16-byte accesses.
+__global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate_up,
+                                       long long total_chunks, int inter) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_chunks) return;
+  const int chunks = inter >> 3;
+  const long long t = i / chunks;
+  const int c = (int)(i - t * chunks);
+  const uint4 g4 = *(const uint4*)(gate_up + t * 2 * inter + c * 8);
+  const uint4 u4 = *(const uint4*)(gate_up + t * 2 * inter + inter + c * 8);
+  const __nv_bfloat162* g = (const __nv_bfloat162*)&g4;
+  const __nv_bfloat162* u = (const __nv_bfloat162*)&u4;
+  uint4 packed;
+  __nv_bfloat162* o = (__nv_bfloat162*)&packed;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 gf = __bfloat1622float2(g[e]), uf = __bfloat1622float2(u[e]);
+    o[e] = __floats2bfloat162_rn(gf.x / (1.f + expf(-gf.x)) * uf.x, gf.y / (1.f + expf(-gf.y)) * uf.y);
+  }
+  *(uint4*)(out + t * inter + c * 8) = packed;
+}
+
 PAE_EXPORT int pae_silu_mul(void* out, const void* gate_up, int tokens, int inter, int dtype, void* stream) {
   const long long n = (long long)tokens * inter;
   if (n == 0) return 0;
+  if (dtype == kBF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    const long long chunks = n / 8;
+    launch_kernel(silu_mul_bf16x8_kernel, (unsigned)((chunks + 255) / 256), 256, 0, (cudaStream_t)stream, 
+        (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, chunks, inter);
+    return check_launch("silu_mul");
+  }
   const unsigned blocks = (unsigned)((n + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    silu_mul_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gate_up, n, inter);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, n, inter);
   else if (dtype == kBF16)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, inter);
+    launch_kernel(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, inter);
   else
     return fail(1, "silu_mul: unknown dtype %d", dtype);
   return check_launch("silu_mul");

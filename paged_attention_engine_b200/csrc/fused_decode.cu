@@ -1,0 +1,195 @@
+// Kernels that finish a split-K product inside the kernel that consumes it.
+//
+// In a step of few tokens the tcgen05 products leave float32 partial sums
+// partial[split, token, n] (gemm_tcgen05.cu, SWAPPED form). Summing them is memory-trivial
+// but a launch of its own; a decode step is bound by its number of launches, so the sum is
+// folded into what comes next in the layer:
+//
+//   sum + residual -> new residual stream, and its RMSNorm        (after o_proj, down_proj)
+//   sum -> SiLU(gate) x up                                        (after gate|up)
+//   sum + bias -> rotation of q and k, page write of k and v      (after q|k|v)
+//
+// Every kernel sums the splits in their order, adds bias then residual in float32 and rounds
+// the sum to the engine dtype before it goes on, exactly as the stand-alone reduction
+// (pae_reduce_splits) followed by the stand-alone kernel does: the fused and the unfused
+// paths give the same bits.
+#include "common.cuh"
+
+using namespace pae;
+
+namespace {
+
+__device__ __forceinline__ float split_sum(const float* __restrict__ partial, int splits, size_t plane, size_t at) {
+  float v = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < splits; ++s) v += partial[(size_t)s * plane + at];
+  return v;
+}
+
+// value[row, :] = round(sum of splits + bias + residual); normed[row, :] = RMSNorm(value[row, :]) * weight.
+template <typename T>
+__global__ void __launch_bounds__(512) splitk_rms_norm_kernel(T* __restrict__ normed, T* __restrict__ value,
+                                                              const float* __restrict__ partial, int splits,
+                                                              const float* __restrict__ bias, const T* __restrict__ residual,
+                                                              const float* __restrict__ weight, int rows, int width, float eps) {
+  dependent_launch_prologue();
+  extern __shared__ float row_values[];       // [width]: the rounded sums of this row
+  __shared__ float reduce[32];
+  const int row = blockIdx.x;
+  const size_t plane = (size_t)rows * width;
+  float squares = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const size_t at = (size_t)row * width + i;
+    float v = split_sum(partial, splits, plane, at);
+    if (bias != nullptr) v += bias[i];
+    if (residual != nullptr) v += to_float(residual[at]);
+    const T rounded = from_float<T>(v);
+    value[at] = rounded;
+    const float r = to_float(rounded);
+    row_values[i] = r;
+    squares += r * r;
+  }
+  squares = warp_sum(squares);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) reduce[warp] = squares;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < warps ? reduce[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) reduce[0] = rsqrtf(v / (float)width + eps);
+  }
+  __syncthreads();
+  const float scale = reduce[0];
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    normed[(size_t)row * width + i] = from_float<T>(row_values[i] * scale * weight[i]);
+}
+
+// out[t, i] = silu(g) * u with g, u the rounded sums of columns i and inter + i.
+template <typename T>
+__global__ void splitk_silu_mul_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int tokens,
+                                       int inter) {
+  dependent_launch_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * inter) return;
+  const long long t = i / inter;
+  const int c = (int)(i - t * inter);
+  const size_t plane = (size_t)tokens * 2 * inter;
+  const float g = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + c)));
+  const float u = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + inter + c)));
+  out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
+// qkv[t, head, :] = round(sum + bias), q and k rotated, k and v written to their pages
+// (same arithmetic as rotary_qk_cache_write_kernel of elementwise.cu).
+template <typename T>
+__global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const float* __restrict__ partial, int splits,
+                                                 const float* __restrict__ bias, const float* __restrict__ table,
+                                                 const int* __restrict__ slots, T* __restrict__ keys, T* __restrict__ values,
+                                                 int tokens, int heads, int kv_heads, int d, int page_size) {
+  dependent_launch_prologue();
+  const int half = d >> 1;
+  const int all_heads = heads + 2 * kv_heads;
+  const int per_token = all_heads * half;
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)tokens * per_token) return;
+  const int t = (int)(i / per_token);
+  const int rest = (int)(i - (long long)t * per_token);
+  const int head = rest / half, f = rest - head * half;
+  const size_t plane = (size_t)tokens * all_heads * d;
+  const size_t at = ((size_t)t * all_heads + head) * d;
+  float lo = split_sum(partial, splits, plane, at + f);
+  float hi = split_sum(partial, splits, plane, at + f + half);
+  if (bias != nullptr) {
+    lo += bias[head * d + f];
+    hi += bias[head * d + f + half];
+  }
+  lo = to_float(from_float<T>(lo));
+  hi = to_float(from_float<T>(hi));
+  if (head < heads + kv_heads && table != nullptr) {
+    const float c = table[(size_t)t * d + f], s = table[(size_t)t * d + half + f];
+    const float new_lo = lo * c - hi * s;
+    const float new_hi = hi * c + lo * s;
+    lo = new_lo;
+    hi = new_hi;
+  }
+  qkv[at + f] = from_float<T>(lo);
+  qkv[at + f + half] = from_float<T>(hi);
+  if (head >= heads && slots != nullptr) {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int page = slot / page_size, offset = slot - page * page_size;
+    const bool is_key = head < heads + kv_heads;
+    const int kv_head = is_key ? head - heads : head - heads - kv_heads;
+    T* to = (is_key ? keys : values) + (((size_t)page * kv_heads + kv_head) * page_size + offset) * d;
+    to[f] = from_float<T>(lo);
+    to[f + half] = from_float<T>(hi);
+  }
+}
+
+}  // namespace
+
+PAE_EXPORT int pae_splitk_rms_norm(void* normed, void* value, const float* partial, int splits, const float* bias,
+                                   const void* residual, const float* weight, int rows, int width, float eps, int dtype,
+                                   void* stream) {
+  if (rows == 0) return 0;
+  if ((size_t)width * sizeof(float) > 160 * 1024) return fail(2, "splitk_rms_norm: rows of %d do not fit shared memory", width);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t bytes = (size_t)width * sizeof(float);
+  const int threads = width >= 1024 ? 512 : (width >= 256 ? 256 : 64);
+  if (dtype == kBF16) {
+    auto kernel = splitk_rms_norm_kernel<__nv_bfloat16>;
+    static bool raised = false;
+    if (bytes > 48 * 1024 && !raised) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      raised = true;
+    }
+    launch_kernel(kernel, rows, threads, bytes, s, (__nv_bfloat16*)normed, (__nv_bfloat16*)value, partial, splits, bias,
+                                        (const __nv_bfloat16*)residual, weight, rows, width, eps);
+  } else if (dtype == kF32) {
+    auto kernel = splitk_rms_norm_kernel<float>;
+    static bool raised = false;
+    if (bytes > 48 * 1024 && !raised) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      raised = true;
+    }
+    launch_kernel(kernel, rows, threads, bytes, s, (float*)normed, (float*)value, partial, splits, bias, (const float*)residual, weight,
+                                        rows, width, eps);
+  } else {
+    return fail(1, "splitk_rms_norm: unknown dtype %d", dtype);
+  }
+  return check_launch("splitk_rms_norm");
+}
+
+PAE_EXPORT int pae_splitk_silu_mul(void* out, const float* partial, int splits, int tokens, int inter, int dtype,
+                                   void* stream) {
+  const long long n = (long long)tokens * inter;
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kBF16)
+    launch_kernel(splitk_silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, splits, tokens, inter);
+  else if (dtype == kF32)
+    launch_kernel(splitk_silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, partial, splits, tokens, inter);
+  else
+    return fail(1, "splitk_silu_mul: unknown dtype %d", dtype);
+  return check_launch("splitk_silu_mul");
+}
+
+PAE_EXPORT int pae_splitk_rotary_cache_write(void* qkv, const float* partial, int splits, const float* bias,
+                                             const float* table, const int* slots, void* keys, void* values, int tokens,
+                                             int heads, int kv_heads, int d, int page_size, int dtype, void* stream) {
+  if (d % 2) return fail(2, "splitk_rotary_cache_write: head_dim %d is odd", d);
+  const long long n = (long long)tokens * (heads + 2 * kv_heads) * (d / 2);
+  if (n == 0) return 0;
+  const unsigned blocks = (unsigned)((n + 127) / 128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kBF16)
+    launch_kernel(splitk_rotary_cache_write_kernel<__nv_bfloat16>, blocks, 128, 0, s, (__nv_bfloat16*)qkv, partial, splits, bias, table, slots, (__nv_bfloat16*)keys, (__nv_bfloat16*)values, tokens, heads, kv_heads, d, page_size);
+  else if (dtype == kF32)
+    launch_kernel(splitk_rotary_cache_write_kernel<float>, blocks, 128, 0, s, (float*)qkv, partial, splits, bias, table, slots, (float*)keys, (float*)values, tokens, heads, kv_heads, d, page_size);
+  else
+    return fail(1, "splitk_rotary_cache_write: unknown dtype %d", dtype);
+  return check_launch("splitk_rotary_cache_write");
+}
+
+PAE_DEFINE_LAST_ERROR()

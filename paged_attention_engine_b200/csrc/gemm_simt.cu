@@ -22,6 +22,7 @@ template <typename TA, typename TW, typename TO>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(TO* __restrict__ out, const TA* __restrict__ x,
                                                         const TW* __restrict__ w, const float* __restrict__ bias,
                                                         const TO* __restrict__ residual, int M, int N, int K) {
+  dependent_launch_prologue();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -82,7 +83,7 @@ template <typename TA, typename TW, typename TO>
 int launch(void* out, const void* x, const void* w, const float* bias, const void* residual, int M, int N, int K,
            cudaStream_t s) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_simt_kernel<TA, TW, TO><<<grid, 256, 0, s>>>((TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K);
+  launch_kernel(gemm_simt_kernel<TA, TW, TO>, grid, 256, 0, s, (TO*)out, (const TA*)x, (const TW*)w, bias, (const TO*)residual, M, N, K);
   return check_launch("linear_simt");
 }
 

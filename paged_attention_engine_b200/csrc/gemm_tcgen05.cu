@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   volatile uint32_t* tmem_holder = (volatile uint32_t*)(generic_base + T::STAGES * T::STAGE_BYTES + 8 * (2 * T::STAGES + 1));
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
 
+  dependent_launch_trigger();     // the kernel after this one may begin its own set-up
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y;
   const int kb_begin = blockIdx.z * p.kb_per_split;
@@ -217,6 +218,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Barriers and tensor memory are set up; from here on global memory is touched, which has
+  // to wait for the kernel before this one.
+  dependent_launch_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -434,7 +438,7 @@ int launch(const Params& p, const void* a, const void* b, int k, int splits, cud
     configured = true;
   }
   dim3 grid((p.rows_a + BM - 1) / BM, (p.rows_b + BN - 1) / BN, splits);
-  kernel<<<grid, THREADS, T::SMEM_BYTES, stream>>>(map_a, map_b, p);
+  launch_kernel(kernel, grid, THREADS, T::SMEM_BYTES, stream, map_a, map_b, p);
   return check_launch("linear_tcgen05");
 }
 
@@ -508,6 +512,7 @@ PAE_EXPORT int pae_linear_tcgen05_swapped(float* partial, const void* x, const v
 template <typename TO>
 __global__ void reduce_splits_kernel(TO* __restrict__ out, const float* __restrict__ partial, const float* __restrict__ bias,
                                      const TO* __restrict__ residual, int splits, long long plane, int n) {
+  dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= plane) return;
   float v = 0.f;
@@ -524,9 +529,9 @@ PAE_EXPORT int pae_reduce_splits(void* out, const float* partial, const float* b
   const unsigned blocks = (unsigned)((plane + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (out_f32)
-    reduce_splits_kernel<float><<<blocks, 256, 0, s>>>((float*)out, partial, bias, (const float*)residual, splits, plane, n);
+    launch_kernel(reduce_splits_kernel<float>, blocks, 256, 0, s, (float*)out, partial, bias, (const float*)residual, splits, plane, n);
   else
-    reduce_splits_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, partial, bias, (const __nv_bfloat16*)residual, splits, plane, n);
+    launch_kernel(reduce_splits_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, bias, (const __nv_bfloat16*)residual, splits, plane, n);
   return check_launch("reduce_splits");
 }
 

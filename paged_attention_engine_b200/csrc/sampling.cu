@@ -29,15 +29,58 @@ __device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
 }
 
 constexpr int THREADS = 512;
+constexpr int CHUNK = 4096;      // vocabulary entries per block of the first stage
 
-__global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits,
-                                                         const float* __restrict__ temperature,
-                                                         const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
-                                                         const int* __restrict__ request_key,
-                                                         const int* __restrict__ output_index, int vocab) {
+struct Best {
+  float value;
+  int index;
+};
+
+__device__ __forceinline__ Best block_best(float v_best, int i_best, float* best_v, int* best_i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
+    if (better(ov, oi, v_best, i_best)) {
+      v_best = ov;
+      i_best = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) {
+    best_v[warp] = v_best;
+    best_i[warp] = i_best;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    v_best = lane < warps ? best_v[lane] : -FLT_MAX;
+    i_best = lane < warps ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
+      if (better(ov, oi, v_best, i_best)) {
+        v_best = ov;
+        i_best = oi;
+      }
+    }
+  }
+  return Best{v_best, i_best};      // valid in lane 0 of warp 0
+}
+
+// First stage: the best candidate of one chunk of one row. With a single chunk the token is
+// written at once.
+__global__ void __launch_bounds__(THREADS) sample_chunks_kernel(int* __restrict__ tokens, float* __restrict__ chunk_value,
+                                                                int* __restrict__ chunk_index,
+                                                                const float* __restrict__ logits,
+                                                                const float* __restrict__ temperature,
+                                                                const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
+                                                                const int* __restrict__ request_key,
+                                                                const int* __restrict__ output_index, int vocab, int chunks) {
+  dependent_launch_prologue();
   __shared__ float best_v[THREADS / 32];
   __shared__ int best_i[THREADS / 32];
-  const int r = blockIdx.x;
+  const int r = blockIdx.y, chunk = blockIdx.x;
   const float* row = logits + (size_t)r * vocab;
   const float t = temperature[r];
   uint32_t h = 0;
@@ -50,7 +93,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ token
   const float inv_t = t > 0.f ? 1.f / t : 1.f;
   float v_best = -FLT_MAX;
   int i_best = 0x7fffffff;
-  for (int j = threadIdx.x; j < vocab; j += THREADS) {
+  const int end = min(vocab, (chunk + 1) * CHUNK);
+  for (int j = chunk * CHUNK + threadIdx.x; j < end; j += THREADS) {
     float v = row[j];
     if (t > 0.f) {
       const uint32_t hv = mix32(h + (uint32_t)j * 0x9E3779B1u);
@@ -62,48 +106,68 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(int* __restrict__ token
       i_best = j;
     }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
-    if (better(ov, oi, v_best, i_best)) {
-      v_best = ov;
-      i_best = oi;
+  const Best best = block_best(v_best, i_best, best_v, best_i);
+  if (threadIdx.x == 0) {
+    if (chunks == 1) {
+      tokens[r] = best.index == 0x7fffffff ? 0 : best.index;
+    } else {
+      chunk_value[(size_t)r * chunks + chunk] = best.value;
+      chunk_index[(size_t)r * chunks + chunk] = best.index;
     }
   }
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane == 0) {
-    best_v[warp] = v_best;
-    best_i[warp] = i_best;
-  }
-  __syncthreads();
-  if (warp == 0) {
-    v_best = lane < THREADS / 32 ? best_v[lane] : -FLT_MAX;
-    i_best = lane < THREADS / 32 ? best_i[lane] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, v_best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, i_best, o);
-      if (better(ov, oi, v_best, i_best)) {
-        v_best = ov;
-        i_best = oi;
-      }
+}
+
+// Second stage: the best of a row's chunks (ties to the lowest index, as within a chunk).
+__global__ void sample_rows_kernel(int* __restrict__ tokens, const float* __restrict__ chunk_value,
+                                   const int* __restrict__ chunk_index, int chunks) {
+  dependent_launch_prologue();
+  __shared__ float best_v[4];
+  __shared__ int best_i[4];
+  const int r = blockIdx.x;
+  float v_best = -FLT_MAX;
+  int i_best = 0x7fffffff;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    const float v = chunk_value[(size_t)r * chunks + c];
+    const int i = chunk_index[(size_t)r * chunks + c];
+    if (better(v, i, v_best, i_best)) {
+      v_best = v;
+      i_best = i;
     }
-    if (lane == 0) tokens[r] = i_best == 0x7fffffff ? 0 : i_best;
   }
+  const Best best = block_best(v_best, i_best, best_v, best_i);
+  if (threadIdx.x == 0) tokens[r] = best.index == 0x7fffffff ? 0 : best.index;
 }
 
 }  // namespace
 
+// Words (4 bytes each) of scratch that pae_sample needs.
+PAE_EXPORT long long pae_sample_scratch_words(int rows, int vocab) {
+  const int chunks = (vocab + CHUNK - 1) / CHUNK;
+  return chunks > 1 ? 2LL * rows * chunks : 0;
+}
+
 // tokens int32 [rows]; logits float32 [rows, vocab]; per row: temperature (float32),
 // the two halves of the 64-bit seed, the request's key and the index of the output token.
+// `scratch` holds pae_sample_scratch_words(rows, vocab) words (may be null when that is 0).
 PAE_EXPORT int pae_sample(int* tokens, const float* logits, const float* temperature, const int* seed_lo,
                           const int* seed_hi, const int* request_key, const int* output_index, int rows, int vocab,
-                          void* stream) {
+                          void* scratch, void* stream) {
   if (rows == 0) return 0;
   if (vocab < 1) return fail(2, "sample: vocabulary of %d", vocab);
-  sample_kernel<<<rows, THREADS, 0, (cudaStream_t)stream>>>(tokens, logits, temperature, seed_lo, seed_hi, request_key, output_index, vocab);
-  return check_launch("sample");
+  if (rows > 65535) return fail(3, "sample: %d rows are more than one launch takes", rows);
+  const int chunks = (vocab + CHUNK - 1) / CHUNK;
+  if (chunks > 1 && scratch == nullptr) return fail(2, "sample: no scratch for %d chunks", chunks);
+  float* chunk_value = (float*)scratch;
+  int* chunk_index = (int*)scratch + (size_t)rows * chunks;
+  cudaStream_t s = (cudaStream_t)stream;
+  launch_kernel(sample_chunks_kernel, dim3(chunks, rows), THREADS, 0, s, tokens, chunk_value, chunk_index, logits, temperature, seed_lo,
+                                                             seed_hi, request_key, output_index, vocab, chunks);
+  if (int err = check_launch("sample")) return err;
+  if (chunks > 1) {
+    launch_kernel(sample_rows_kernel, rows, 128, 0, s, tokens, chunk_value, chunk_index, chunks);
+    return check_launch("sample");
+  }
+  return 0;
 }
 
 PAE_DEFINE_LAST_ERROR()

@@ -49,6 +49,8 @@ def _lib(name: str) -> ctypes.CDLL:
         lib.pae_last_error.restype = ctypes.c_char_p
         if name == "attention_mma":
             lib.pae_decode_scratch_floats.restype = ctypes.c_longlong
+        if name == "sampling":
+            lib.pae_sample_scratch_words.restype = ctypes.c_longlong
         _libs[name] = lib
     return lib
 
@@ -94,7 +96,46 @@ def _need(t: torch.Tensor, what: str, dtype=None) -> None:
 
 # ----------------------------------------------------------------------------------- #
 
-def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+class PendingSum:
+    """A split-K product whose float32 partial sums [splits, M, N] have not been added up yet.
+
+    `linear` returns one for a step of few tokens. `rms_norm`, `silu_mul` and
+    `rotary_qk_cache_write` add the splits up inside their own kernel (bias and residual
+    included), which saves a launch; anything else calls `materialized`, which runs the
+    stand-alone reduction once and keeps its result in `value`."""
+
+    def __init__(self, partial, bias, residual, out_dtype):
+        self.partial = partial
+        self.bias = bias
+        self.residual = residual
+        self.dtype = out_dtype
+        self.value = None
+
+    @property
+    def shape(self):
+        return self.partial.shape[1:]
+
+    @property
+    def device(self):
+        return self.partial.device
+
+
+def materialized(x):
+    """The tensor that `x` stands for (x itself unless it is a PendingSum)."""
+    if not isinstance(x, PendingSum):
+        return x
+    if x.value is None:
+        splits, m, n = x.partial.shape
+        out = torch.empty((m, n), dtype=x.dtype, device=x.partial.device)
+        lib = _lib("gemm_tcgen05")
+        _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(x.partial), _ptr(x.bias), _ptr(x.residual), c_int(splits),
+                                          c_int(m), c_int(n), c_int(1 if x.dtype == torch.float32 else 0), _stream()))
+        x.value = out
+    return x.value
+
+
+def gather_rows(x, rows: torch.Tensor) -> torch.Tensor:
+    x = materialized(x)
     _need(x, "gather_rows: x")
     _need(rows, "gather_rows: rows", torch.int32)
     out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
@@ -108,11 +149,22 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return gather_rows(table, ids)
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    _need(x, "rms_norm: x")
+def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
     _need(weight, "rms_norm: weight", torch.float32)
     if weight.numel() != x.shape[-1]:
         raise KernelError(f"rms_norm: weight of {weight.numel()} for rows of {x.shape[-1]}")
+    if isinstance(x, PendingSum) and x.value is None:
+        splits, m, n = x.partial.shape
+        value = torch.empty((m, n), dtype=x.dtype, device=x.device)
+        normed = torch.empty_like(value)
+        lib = _lib("fused_decode")
+        _check(lib, lib.pae_splitk_rms_norm(_ptr(normed), _ptr(value), _ptr(x.partial), c_int(splits), _ptr(x.bias),
+                                            _ptr(x.residual), _ptr(weight), c_int(m), c_int(n), c_float(eps),
+                                            c_int(_DTYPE_CODE[x.dtype]), _stream()))
+        x.value = value
+        return normed
+    x = materialized(x)
+    _need(x, "rms_norm: x")
     out = torch.empty_like(x)
     lib = _lib("elementwise")
     rows = x.numel() // x.shape[-1] if x.numel() else 0
@@ -124,6 +176,8 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 # The bfloat16 products run on the tcgen05 kernels when the shape allows; set to False to
 # send everything to the CUDA-core kernel (tests compare the two).
 use_tensor_cores = True
+# Whether a split-K product is summed inside the kernel that consumes it (tests compare both).
+fuse_split_sums = True
 SWAPPED_MAX_TOKENS = 64
 
 _error_flags: dict[int, torch.Tensor] = {}
@@ -163,6 +217,8 @@ def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
 
 def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]."""
+    x = materialized(x)
+    residual = materialized(residual)
     _need(x, "linear: x")
     _need(weight, "linear: weight")
     m, k = x.shape
@@ -201,10 +257,8 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch
                                                    _ptr(flag), _stream()))
         if splits == 1 and bias is None and residual is None and out_dtype == torch.float32:
             return partial[0]
-        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(partial), _ptr(bias), _ptr(residual), c_int(splits), c_int(m),
-                                          c_int(n), out_f32, _stream()))
-        return out
+        pending = PendingSum(partial, bias, residual, out_dtype)
+        return pending if fuse_split_sums else materialized(pending)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
                                        c_int(k), out_f32, _ptr(flag), _stream()))
@@ -222,11 +276,13 @@ def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tenso
     return table
 
 
-def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_heads, head_dim, page_size) -> None:
-    _need(qkv, "rotary_qk_cache_write: qkv")
-    tokens = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_heads, head_dim, page_size) -> torch.Tensor:
+    """Rotates q and k of the fused projection's output (in place), writes k and v to their
+    pages, and returns the [tokens, (heads + 2 kv_heads) * head_dim] tensor."""
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width:
         raise KernelError(f"rotary_qk_cache_write: qkv rows of {qkv.shape[1]} for {num_heads}+2x{num_kv_heads} heads of {head_dim}")
+    tokens = qkv.shape[0]
     if table is not None:
         _need(table, "rotary_qk_cache_write: table", torch.float32)
         if tuple(table.shape) != (tokens, head_dim):
@@ -235,11 +291,25 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         _need(slots, "rotary_qk_cache_write: slots", torch.int32)
         _need(keys, "rotary_qk_cache_write: keys", qkv.dtype)
         _need(values, "rotary_qk_cache_write: values", qkv.dtype)
+    key_ptr = _ptr(keys if slots is not None else None)
+    value_ptr = _ptr(values if slots is not None else None)
+    if isinstance(qkv, PendingSum) and qkv.value is None and qkv.residual is None:
+        splits = qkv.partial.shape[0]
+        out = torch.empty((tokens, width), dtype=qkv.dtype, device=qkv.device)
+        lib = _lib("fused_decode")
+        _check(lib, lib.pae_splitk_rotary_cache_write(
+            _ptr(out), _ptr(qkv.partial), c_int(splits), _ptr(qkv.bias), _ptr(table), _ptr(slots), key_ptr, value_ptr,
+            c_int(tokens), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+            c_int(_DTYPE_CODE[qkv.dtype]), _stream()))
+        qkv.value = out
+        return out
+    qkv = materialized(qkv)
+    _need(qkv, "rotary_qk_cache_write: qkv")
     lib = _lib("elementwise")
     _check(lib, lib.pae_rotary_qk_cache_write(
-        _ptr(qkv), _ptr(table), _ptr(slots), _ptr(keys if slots is not None else None),
-        _ptr(values if slots is not None else None), c_int(tokens), c_int(num_heads), c_int(num_kv_heads),
+        _ptr(qkv), _ptr(table), _ptr(slots), key_ptr, value_ptr, c_int(tokens), c_int(num_heads), c_int(num_kv_heads),
         c_int(head_dim), c_int(page_size), c_int(_code(qkv)), _stream()))
+    return qkv
 
 
 def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int) -> tuple[int, int]:
@@ -256,6 +326,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     """Attention of every token of the step over its request's pages. `num_single` is the number
     of requests that bring exactly one token when the caller knows it (it decides which kernels
     are launched; None launches whatever may be needed)."""
+    qkv = materialized(qkv)
     _need(qkv, "paged_attention: qkv")
     _need(keys, "paged_attention: keys", qkv.dtype)
     _need(values, "paged_attention: values", qkv.dtype)
@@ -292,11 +363,19 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     return out
 
 
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
-    _need(gate_up, "silu_mul: gate_up")
+def silu_mul(gate_up) -> torch.Tensor:
     tokens, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError(f"silu_mul: rows of {two_i} do not split into gate and up")
+    if isinstance(gate_up, PendingSum) and gate_up.value is None and gate_up.bias is None and gate_up.residual is None:
+        splits = gate_up.partial.shape[0]
+        out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+        lib = _lib("fused_decode")
+        _check(lib, lib.pae_splitk_silu_mul(_ptr(out), _ptr(gate_up.partial), c_int(splits), c_int(tokens),
+                                            c_int(two_i // 2), c_int(_DTYPE_CODE[gate_up.dtype]), _stream()))
+        return out
+    gate_up = materialized(gate_up)
+    _need(gate_up, "silu_mul: gate_up")
     out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("elementwise")
     _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), c_int(tokens), c_int(two_i // 2), c_int(_code(gate_up)), _stream()))
@@ -312,6 +391,9 @@ def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> 
     rows, vocab = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     lib = _lib("sampling")
+    words = lib.pae_sample_scratch_words(c_int(rows), c_int(vocab))
+    scratch = torch.empty(words, dtype=torch.int32, device=logits.device) if words else None
     _check(lib, lib.pae_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
-                               _ptr(request_key), _ptr(output_index), c_int(rows), c_int(vocab), _stream()))
+                               _ptr(request_key), _ptr(output_index), c_int(rows), c_int(vocab), _ptr(scratch),
+                               _stream()), 2 if words else 1)
     return out

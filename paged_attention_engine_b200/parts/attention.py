@@ -68,7 +68,7 @@ class GQAAttention(Part):
         group = ctx.groups[cache.group]
         qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
         table = self.position_encoding.table(ctx) if self.position_encoding is not None else None
-        ops.rotary_qk_cache_write(
+        qkv = ops.rotary_qk_cache_write(
             qkv, table, group.slots if cache.writes else None, cache.keys, cache.values,
             self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
         )

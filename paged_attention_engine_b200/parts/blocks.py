@@ -10,5 +10,9 @@ from .base import BLOCKS
 @BLOCKS.register("pre_norm_residual")
 class PreNormResidual:
     def forward(self, ctx, hidden, layer, cache):
-        hidden = layer.mixer.forward(ctx, layer.mixer_norm.forward(ctx, hidden), hidden, cache)
-        return layer.feed_forward.forward(ctx, layer.feed_forward_norm.forward(ctx, hidden), hidden)
+        # `hidden` may be a product that is still to be summed; the norm's kernel sums it, and
+        # `materialized` then hands out the summed tensor without another launch.
+        normed = layer.mixer_norm.forward(ctx, hidden)
+        hidden = layer.mixer.forward(ctx, normed, ctx.ops.materialized(hidden), cache)
+        normed = layer.feed_forward_norm.forward(ctx, hidden)
+        return layer.feed_forward.forward(ctx, normed, ctx.ops.materialized(hidden))

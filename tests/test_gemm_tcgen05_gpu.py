@@ -29,7 +29,7 @@ def _check(ops, m, n, k, bias, residual, out_dtype):
     r = None
     if residual:
         r = _rand((m, n), 3) if out_dtype == torch.bfloat16 else torch.randn(m, n).cuda()
-    got = ops.linear(x, w, b, r, out_dtype=out_dtype)
+    got = ops.materialized(ops.linear(x, w, b, r, out_dtype=out_dtype))
     ops.check_device_errors()
     want = ref.linear(x.cpu(), w.cpu(), None if b is None else b.cpu(), None if r is None else r.cpu(), out_dtype=torch.float32)
     assert got.dtype == out_dtype and tuple(got.shape) == (m, n)
@@ -58,7 +58,7 @@ def test_float32_logits(ops, m, n, k):
 def test_agrees_with_the_cuda_core_kernel(ops):
     x = _rand((40, 1536), 5)
     w = _rand((1000, 1536), 6, 0.05)
-    fast = ops.linear(x, w)
+    fast = ops.materialized(ops.linear(x, w))
     ops.use_tensor_cores = False
     try:
         slow = ops.linear(x, w)
@@ -71,7 +71,54 @@ def test_a_tokens_product_does_not_depend_on_the_batch(ops):
     """Alone, among 7 others, among 63 others: the same sums in the same order."""
     x = _rand((64, 1536), 7)
     w = _rand((2048, 1536), 8, 0.05)
-    whole = ops.linear(x, w)
+    whole = ops.materialized(ops.linear(x, w))
     for count in (1, 8, 24):
-        part = ops.linear(x[:count].contiguous(), w)
+        part = ops.materialized(ops.linear(x[:count].contiguous(), w))
         assert torch.equal(part, whole[:count]), f"{count} tokens"
+
+
+def _pending(ops, m, n, k, bias, residual, seed):
+    x = _rand((m, k), seed)
+    w = _rand((n, k), seed + 1, 0.05)
+    b = torch.randn(n).cuda() if bias else None
+    r = _rand((m, n), seed + 2) if residual else None
+    ops.fuse_split_sums = True
+    pending = ops.linear(x, w, b, r)
+    assert isinstance(pending, ops.PendingSum), "a step of few tokens leaves its product to be summed"
+    ops.fuse_split_sums = False
+    try:
+        plain = ops.linear(x, w, b, r)
+    finally:
+        ops.fuse_split_sums = True
+    return pending, plain
+
+
+def test_sum_fused_into_rms_norm(ops):
+    pending, plain = _pending(ops, 8, 1536, 8960, bias=False, residual=True, seed=30)
+    weight = (1 + 0.1 * torch.randn(1536)).cuda()
+    normed = ops.rms_norm(pending, weight, 1e-6)
+    assert torch.equal(ops.materialized(pending), plain), "the summed residual stream is the same bits"
+    want = ops.rms_norm(plain, weight, 1e-6)
+    # The two norm kernels add the squares in different orders: one rounding step apart at most.
+    assert (normed.float() - want.float()).abs().max().item() <= 2.0 ** -7 * float(want.float().abs().max())
+
+
+def test_sum_fused_into_silu_mul(ops):
+    pending, plain = _pending(ops, 5, 2 * 176, 96, bias=False, residual=False, seed=40)
+    assert torch.equal(ops.silu_mul(pending), ops.silu_mul(plain))
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page", [(12, 2, 128, 16), (3, 1, 32, 16), (5, 5, 48, 8)])
+def test_sum_fused_into_rotation_and_page_write(ops, heads, kv_heads, d, page):
+    tokens, pages = 7, 6
+    width = (heads + 2 * kv_heads) * d
+    pending, plain = _pending(ops, tokens, width, 264, bias=True, residual=False, seed=50)
+    positions = torch.arange(40, 40 + tokens, dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))).cuda()
+    table = ops.rotary_table(positions, inv_freq)
+    slots = torch.randperm(pages * page)[:tokens].to(torch.int32).cuda()
+    caches = [torch.zeros(pages, kv_heads, page, d, dtype=torch.bfloat16).cuda() for _ in range(4)]
+    fused = ops.rotary_qk_cache_write(pending, table, slots, caches[0], caches[1], heads, kv_heads, d, page)
+    unfused = ops.rotary_qk_cache_write(plain.clone(), table, slots, caches[2], caches[3], heads, kv_heads, d, page)
+    assert torch.equal(fused, unfused)
+    assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])

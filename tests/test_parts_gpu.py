@@ -62,7 +62,7 @@ def test_swiglu_part(runtime_of, dtype):
     }
     part = FEED_FORWARDS.get("swiglu")(spec, {k: v.cuda() for k, v in w.items()}, runtime_of(dtype))
     x, residual = torch.randn(9, hidden).to(dtype), torch.randn(9, hidden).to(dtype)
-    got = part.forward(_Ctx(), x.cuda(), residual.cuda()).float().cpu()
+    got = runtime_of(dtype).ops.materialized(part.forward(_Ctx(), x.cuda(), residual.cuda())).float().cpu()
     want = residual.float() + plain.swiglu(x.float(), *(w[f"ff.{n}_proj.weight"].float() for n in ("gate", "up", "down")))
     assert (got - want).abs().max().item() <= _limit(dtype, want)
 
@@ -144,7 +144,7 @@ def test_attention_part_alone(runtime_of, dtype, window):
     for n in (20, 1, 17, 1, 6):
         manager.reserve("r", n)
         ctx = builder.build([StepEntry("r", [0] * n, ())])
-        got.append(mixer.forward(ctx, x[at : at + n].cuda(), residual[at : at + n].cuda(), cache.entry_cache(0)).float().cpu())
+        got.append(rt.ops.materialized(mixer.forward(ctx, x[at : at + n].cuda(), residual[at : at + n].cuda(), cache.entry_cache(0))).float().cpu())
         manager.advance("r", n)
         at += n
     cfg = plain.PlainConfig(1, hidden, heads, kv_heads, d, 8, 8, 1e-6, 1e4, True, (window,))

@@ -14,6 +14,10 @@ import math
 import torch
 
 
+def materialized(x):
+    return x
+
+
 def embedding(ids, table):
     return table[ids.long()]
 
@@ -54,6 +58,7 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         offset = (slots % page_size).long()
         keys[page, :, offset, :] = view[:, num_heads : num_heads + num_kv_heads]
         values[page, :, offset, :] = view[:, num_heads + num_kv_heads :]
+    return qkv
 
 
 def paged_attention(
