@@ -346,10 +346,32 @@ __global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float
   for (int w = 0; w < warps; ++w) total += reduce[w];
   const float inv = total > 0.f ? 1.f / total : 0.f;
 
+  __syncthreads();      // `reduce` is read above and reused below
+  // Warp w folds slices w, w + warps, ...; a lane owns D / 32 neighbouring dimensions. The
+  // warps' sums are then added in the order of the warps, so the result does not depend on timing.
+  constexpr int PER_LANE = D / 32;
+  float acc[PER_LANE];
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) acc[j] = 0.f;
+#pragma unroll 4
+  for (int s = warp; s < slices; s += warps) {
+    const float w = weights[s];
+    const float* from = part_out + (at + s) * D + lane * PER_LANE;
+    if (PER_LANE == 4) {
+      const float4 p = *(const float4*)from;
+      acc[0] += p.x * w; acc[1] += p.y * w; acc[2] += p.z * w; acc[3] += p.w * w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) acc[j] += from[j] * w;
+    }
+  }
+  float* across = weights + max_slices;          // [warps][D]
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) across[warp * D + lane * PER_LANE + j] = acc[j];
+  __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < slices; ++s) v += part_out[(at + s) * D + d] * weights[s];
+    for (int w = 0; w < warps; ++w) v += across[w * D + d];
     out[((size_t)token * heads + h) * D + d] = __float2bfloat16_rn(v * inv);
   }
 }
@@ -490,8 +512,8 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int seqs, cudaStrea
   dim3 grid((p.max_slices + DECODE_WARPS - 1) / DECODE_WARPS, p.kv_heads, seqs);
   launch_kernel(decode_slices_kernel<D>, grid, DECODE_WARPS * 32, bytes, s, p);
   if (int err = check_launch("paged_attention_decode")) return err;
-  if ((size_t)p.max_slices * sizeof(float) > 40 * 1024) return fail(2, "paged_attention_decode: %d slices are more than the merge takes", p.max_slices);
-  launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), D >= 128 ? 128 : 64, p.max_slices * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
+  if ((size_t)(p.max_slices + 4 * D) * sizeof(float) > 40 * 1024) return fail(2, "paged_attention_decode: %d slices are more than the merge takes", p.max_slices);
+  launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), 128, (p.max_slices + 4 * D) * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
                                                                      p.kv_len, p.heads, p.window, p.slice_keys, p.max_slices);
   return check_launch("paged_attention_merge");
 }

@@ -475,11 +475,14 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
 
 // How many float32 partial planes `pae_linear_tcgen05_swapped` writes for this shape.
 PAE_EXPORT int pae_linear_swapped_splits(int n, int k) {
+  // Two blocks of this form fit on each of the 148 SMs. The work should fill that one wave
+  // (a second, partly filled wave costs a whole block's latency), with at least two k-blocks
+  // per split. The count depends on the weight's shape alone, never on the tokens.
   const int tiles = (n + BM - 1) / BM;
   const int k_blocks = (k + BK - 1) / BK;
-  int splits = (2 * 148 + tiles - 1) / tiles;          // about two blocks for each of the 148 SMs
+  int splits = (2 * 148) / tiles;
   splits = splits < 1 ? 1 : splits;
-  const int most = k_blocks / 2 < 1 ? 1 : k_blocks / 2;  // at least two k-blocks per split
+  const int most = k_blocks / 2 < 1 ? 1 : k_blocks / 2;
   splits = splits > most ? most : splits;
   const int per = (k_blocks + splits - 1) / splits;
   return (k_blocks + per - 1) / per;

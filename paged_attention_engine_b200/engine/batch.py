@@ -69,52 +69,57 @@ class StepContext:
 
 class _Staging:
     """Pinned host buffers that take turns, so that a buffer is not refilled while the
-    copy out of it may still be in flight."""
+    copy out of it may still be in flight. The step's integers are written straight into
+    the pinned buffer and leave it in one copy."""
 
     def __init__(self, device: torch.device, turns: int = 4) -> None:
         self.device = device
         self.pinned = device.type == "cuda"
         self.buffers: list[torch.Tensor | None] = [None] * turns
+        self.views: list[np.ndarray | None] = [None] * turns
         self.events: list[Any] = [None] * turns
         self.turn = 0
 
-    def upload(self, flat: np.ndarray, into: torch.Tensor | None = None) -> torch.Tensor:
-        """Copies `flat` to the device: into `into` (a buffer that kernels of a captured
-        graph read) when given, else into a fresh tensor."""
-        if not self.pinned:
-            fresh = torch.from_numpy(flat.copy())
-            if into is None:
-                return fresh
-            into[: flat.size].copy_(fresh)
-            return into
+    def acquire(self, size: int) -> tuple[int, np.ndarray]:
+        """(turn, int32 host array of at least `size` elements) to be filled, then `commit`ted."""
         i = self.turn
         self.turn = (self.turn + 1) % len(self.buffers)
         if self.events[i] is not None:
             self.events[i].synchronize()
+            self.events[i] = None
         buf = self.buffers[i]
-        if buf is None or buf.numel() < flat.size:
-            buf = torch.empty(max(flat.size, 4096), dtype=torch.int32).pin_memory()
+        if buf is None or buf.numel() < size:
+            buf = torch.empty(max(size, 4096), dtype=torch.int32)
+            if self.pinned:
+                buf = buf.pin_memory()
             self.buffers[i] = buf
-        buf[: flat.size].copy_(torch.from_numpy(flat))
-        out = into if into is not None else torch.empty(flat.size, dtype=torch.int32, device=self.device)
-        out[: flat.size].copy_(buf[: flat.size], non_blocking=True)
+            self.views[i] = buf.numpy()
+        return i, self.views[i]
+
+    def commit(self, turn: int, size: int, into: torch.Tensor | None = None) -> torch.Tensor:
+        """Copies the first `size` elements to the device: into `into` (a buffer that the kernels
+        of a captured graph read) when given, else into a fresh tensor."""
+        buf = self.buffers[turn]
+        if not self.pinned:
+            if into is None:
+                return buf[:size].clone()
+            into[:size].copy_(buf[:size])
+            return into
+        out = into if into is not None else torch.empty(size, dtype=torch.int32, device=self.device)
+        out[:size].copy_(buf[:size], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
-        self.events[i] = event
+        self.events[turn] = event
         return out
 
 
-def _pack(sections: list[np.ndarray]) -> tuple[np.ndarray, list[tuple[int, int]]]:
-    """Concatenates int32 arrays, each starting on a 16-byte boundary."""
-    spans = []
-    total = 0
-    for s in sections:
-        spans.append((total, s.size))
-        total += (s.size + 3) // 4 * 4
-    flat = np.zeros(max(total, 4), dtype=np.int32)
-    for (start, size), s in zip(spans, sections):
-        flat[start : start + size] = s.reshape(-1)
-    return flat, spans
+def _layout(sizes: list[int]) -> tuple[list[int], int]:
+    """Start of each section (each on a 16-byte boundary) and the total, in int32 elements."""
+    starts, total = [], 0
+    for n in sizes:
+        starts.append(total)
+        total += (n + 3) // 4 * 4
+    return starts, max(total, 4)
 
 
 def _signed32(value: int) -> int:
@@ -170,53 +175,76 @@ class BatchBuilder:
             slots_of.append(manager.slot_of(e.key))
 
         b = len(entries)
-        q_start = np.zeros(b + 1, dtype=np.int32)
-        np.cumsum(q_lens, out=q_start[1:])
-        total = int(q_start[-1])
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        if self.vocab_size is not None and ((token_ids < 0) | (token_ids >= self.vocab_size)).any():
+        decode_only = all(n == 1 for n in q_lens)
+        total = b if decode_only else sum(q_lens)
+        pos0_arr = np.asarray(pos0, dtype=np.int32)
+        if decode_only:
+            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=b)
+            seq_index = np.arange(b, dtype=np.int32)
+            positions = pos0_arr
+            q_start = np.arange(b + 1, dtype=np.int32)
+            kv_len = pos0_arr + 1
+        else:
+            q_start = np.zeros(b + 1, dtype=np.int32)
+            np.cumsum(q_lens, out=q_start[1:])
+            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+            seq_index = np.repeat(np.arange(b, dtype=np.int32), q_lens)
+            positions = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
+            kv_len = pos0_arr + np.asarray(q_lens, dtype=np.int32)
+        if self.vocab_size is not None and (int(token_ids.min()) < 0 or int(token_ids.max()) >= self.vocab_size):
             bad = int(token_ids[(token_ids < 0) | (token_ids >= self.vocab_size)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
-        seq_index = np.repeat(np.arange(b, dtype=np.int32), q_lens)
-        positions = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
-        kv_len = np.asarray(pos0, dtype=np.int32) + np.asarray(q_lens, dtype=np.int32)
         rows = [int(q_start[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
-        logit_rows = np.asarray(rows, dtype=np.int32)
 
-        sections = [
-            token_ids, positions, seq_index, q_start, np.asarray(pos0, dtype=np.int32), kv_len,
-            np.asarray(slots_of, dtype=np.int32), logit_rows,
-        ]
         max_kv = int(kv_len.max())
         width = (max_kv + page - 1) // page
         if table_width is not None:
             if table_width < width:
                 raise ValueError(f"block tables of {width} pages do not fit the fixed width {table_width}")
             width = table_width
-        for g in range(len(manager.groups)):
+        num_groups = len(manager.groups)
+        if sampling is not None and len(sampling) != len(rows):
+            raise ValueError(f"{len(sampling)} sampling rows for {len(rows)} wanted places")
+        sizes = [total, total, total, b + 1, b, b, b, len(rows)] + [b * width, total] * num_groups
+        first_sampling = len(sizes)
+        if sampling is not None:
+            sizes += [len(rows)] * 5
+        starts, size = _layout(sizes)
+        turn, host = self.staging.acquire(size)
+
+        def put(i: int, values) -> None:
+            host[starts[i] : starts[i] + sizes[i]] = values
+
+        put(0, token_ids)
+        put(1, positions)
+        put(2, seq_index)
+        put(3, q_start)
+        put(4, pos0_arr)
+        put(5, kv_len)
+        put(6, slots_of)
+        put(7, rows)
+        page_index = positions // page
+        offset = positions - page_index * page
+        for g in range(num_groups):
             table = manager.table_rows(g, slots_of, width)
-            page_of_token = table[seq_index, positions // page]
-            if (page_of_token < 0).any():
+            page_of_token = table[seq_index, page_index]
+            if int(page_of_token.min()) < 0:
                 bad = int(np.argmax(page_of_token < 0))
                 raise ValueError(
                     f"request {entries[int(seq_index[bad])].key!r}: position {int(positions[bad])} has no page in group {g}"
                 )
-            sections += [np.ascontiguousarray(table), page_of_token * page + positions % page]
-        first_sampling = len(sections)
+            host[starts[8 + 2 * g] : starts[8 + 2 * g] + b * width].reshape(b, width)[:] = table
+            put(9 + 2 * g, page_of_token * page + offset)
         if sampling is not None:
-            if len(sampling) != len(rows):
-                raise ValueError(f"{len(sampling)} sampling rows for {len(rows)} wanted places")
-            sections += [
-                np.asarray([r.temperature for r in sampling], dtype=np.float32).view(np.int32),
-                np.asarray([_signed32(r.seed) for r in sampling], dtype=np.int32),
-                np.asarray([_signed32(r.seed >> 32) for r in sampling], dtype=np.int32),
-                np.asarray([_signed32(r.request_key) for r in sampling], dtype=np.int32),
-                np.asarray([_signed32(r.output_index) for r in sampling], dtype=np.int32),
-            ]
-
-        flat, spans = _pack(sections)
-        dev = self.staging.upload(flat, into)
-        self.bytes_uploaded = 4 * flat.size
+            f = first_sampling
+            host[starts[f] : starts[f] + len(rows)].view(np.float32)[:] = [r.temperature for r in sampling]
+            put(f + 1, [_signed32(r.seed) for r in sampling])
+            put(f + 2, [_signed32(r.seed >> 32) for r in sampling])
+            put(f + 3, [_signed32(r.request_key) for r in sampling])
+            put(f + 4, [_signed32(r.output_index) for r in sampling])
+        dev = self.staging.commit(turn, size, into)
+        self.bytes_uploaded = 4 * size
+        spans = list(zip(starts, sizes))
 
         def part(i: int) -> torch.Tensor:
             start, size = spans[i]

@@ -137,6 +137,17 @@ class Sequence:
     def history_len(self) -> int:
         return self.request.prompt_len + len(self.generated)
 
+    def history_slice(self, start: int, count: int) -> tuple[int, ...]:
+        """Tokens start .. start + count - 1 of the history, without building all of it."""
+        prompt = self.request.prompt_token_ids
+        n = len(prompt)
+        end = start + count
+        if end <= n:
+            return tuple(prompt[start:end])
+        if start >= n:
+            return tuple(self.generated[start - n : end - n])
+        return tuple(prompt[start:]) + tuple(self.generated[: end - n])
+
     @property
     def is_finished(self) -> bool:
         return len(self.generated) >= self.request.max_new_tokens
@@ -271,10 +282,9 @@ class Scheduler:
         """Plans the next tokens of `seq`'s history: as many as the budget has room for."""
         pending = seq.history_len - seq.num_computed
         count = min(pending, self._budget_left)
-        history = seq.history
         self._plan.append(
             ScheduledWork(
-                seq=seq, token_ids=tuple(history[seq.num_computed : seq.num_computed + count]),
+                seq=seq, token_ids=seq.history_slice(seq.num_computed, count),
                 start=seq.num_computed, is_prefill=is_prefill, wants_token=count == pending,
             )
         )
