@@ -65,10 +65,17 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t address)
 }
 
 __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// 2^x by the special-function unit (two units in the last place; flushes denormals).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -144,25 +151,35 @@ __device__ __forceinline__ void accumulate_16_keys(float (*o)[4], const uint32_t
 // lane/4 + 8 (half 1). Returns the probabilities as the A fragment of the next product.
 template <int D, typename Visible>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float* row_max, float* row_sum, float (*o)[4], uint32_t* p,
-                                             float scale_log2, Visible visible) {
+                                             float scale_log2, bool unmasked, Visible visible) {
   const int lane = threadIdx.x & 31;
   const int c = (lane & 3) * 2;
   float block_max[2] = {-FLT_MAX, -FLT_MAX};
+  if (unmasked) {             // the same for the whole warp: every score of the block counts
 #pragma unroll
-  for (int t = 0; t < 2; ++t)
+    for (int t = 0; t < 2; ++t)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int half = j >> 1, key = t * 8 + c + (j & 1);
-      s[t][j] = visible(half, key) ? s[t][j] * scale_log2 : -FLT_MAX;
-      block_max[half] = fmaxf(block_max[half], s[t][j]);
-    }
+      for (int j = 0; j < 4; ++j) {
+        s[t][j] *= scale_log2;
+        block_max[j >> 1] = fmaxf(block_max[j >> 1], s[t][j]);
+      }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 2; ++t)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int half = j >> 1, key = t * 8 + c + (j & 1);
+        s[t][j] = visible(half, key) ? s[t][j] * scale_log2 : -FLT_MAX;
+        block_max[half] = fmaxf(block_max[half], s[t][j]);
+      }
+  }
   float rescale[2];
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     block_max[half] = fmaxf(block_max[half], __shfl_xor_sync(0xffffffffu, block_max[half], 1));
     block_max[half] = fmaxf(block_max[half], __shfl_xor_sync(0xffffffffu, block_max[half], 2));
     const float new_max = fmaxf(row_max[half], block_max[half]);
-    rescale[half] = row_max[half] == -FLT_MAX ? 0.f : exp2f(row_max[half] - new_max);
+    rescale[half] = row_max[half] == -FLT_MAX ? 0.f : fast_exp2(row_max[half] - new_max);
     row_max[half] = new_max;
   }
   float block_sum[2] = {0.f, 0.f};
@@ -171,7 +188,7 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float* row_max, floa
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int half = j >> 1;
-      const float e = s[t][j] == -FLT_MAX ? 0.f : exp2f(s[t][j] - row_max[half]);
+      const float e = s[t][j] == -FLT_MAX ? 0.f : fast_exp2(s[t][j] - row_max[half]);
       s[t][j] = e;
       block_sum[half] += e;
     }
@@ -181,12 +198,16 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float* row_max, floa
     block_sum[half] += __shfl_xor_sync(0xffffffffu, block_sum[half], 2);
     row_sum[half] = row_sum[half] * rescale[half] + block_sum[half];
   }
+  // The running output only has to be rescaled when some row's maximum moved (multiplying
+  // by exactly 1 changes nothing); late in a long row that is rare.
+  if (__any_sync(0xffffffffu, rescale[0] != 1.f || rescale[1] != 1.f)) {
 #pragma unroll
-  for (int n = 0; n < D / 8; ++n) {
-    o[n][0] *= rescale[0];
-    o[n][1] *= rescale[0];
-    o[n][2] *= rescale[1];
-    o[n][3] *= rescale[1];
+    for (int n = 0; n < D / 8; ++n) {
+      o[n][0] *= rescale[0];
+      o[n][1] *= rescale[0];
+      o[n][2] *= rescale[1];
+      o[n][3] *= rescale[1];
+    }
   }
   p[0] = pack_bf16(s[0][0], s[0][1]);
   p[1] = pack_bf16(s[0][2], s[0][3]);
@@ -273,7 +294,7 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const 
     float s[2][4];
     scores_16_keys<D>(s, q, k_tile, 0);
     uint32_t pa[4];
-    softmax_step<D>(s, row_max, row_sum, o, pa, p.scale_log2,
+    softmax_step<D>(s, row_max, row_sum, o, pa, p.scale_log2, key0 >= first_key && key0 + TILE_KEYS <= end,
                     [&](int, int key) { return key0 + key >= first_key && key0 + key < end; });
     accumulate_16_keys<D>(o, pa, k_tile + TILE_BYTES, 0);
     __syncwarp();      // the tile is read; the next iteration's fetch may overwrite the other stage
@@ -398,47 +419,71 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
   dependent_launch_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
-  if (tile * PREFILL_BQ >= q_count || (p.skip_single && q_count == 1)) return;
+  if (p.skip_single && q_count == 1) return;
+  // A block takes two 64-token tiles of its request, the x-th from the end and the x-th from
+  // the start: a late tile sees many keys and an early one few, so every block of a request
+  // has about the same work.
+  const int q_tiles = (q_count + PREFILL_BQ - 1) / PREFILL_BQ;
+  if ((int)blockIdx.x * 2 >= q_tiles) return;
+  const uint32_t smem_base = smem_u32(smem);
+  const int g = h / (p.heads / p.kv_heads);
+  const int row_elems = (p.heads + 2 * p.kv_heads) * D;
+  const int* table = p.block_table + (size_t)b * p.table_width;
+  const int warp_row0 = warp * 16;
+  constexpr int TILE_BYTES = PREFILL_BKEYS * D * 2;
+  constexpr int ROW_CHUNKS = D / 8;
+  constexpr int ROWS_PER_PASS = 128 / ROW_CHUNKS;
+  constexpr int PER_THREAD = PREFILL_BKEYS / ROWS_PER_PASS;
+  const int my_chunk = threadIdx.x % ROW_CHUNKS, my_row = threadIdx.x / ROW_CHUNKS;
+  int dst_offset[PER_THREAD];
+#pragma unroll
+  for (int j = 0; j < PER_THREAD; ++j) dst_offset[j] = TileLayout<D>::offset_bytes(my_row + j * ROWS_PER_PASS, my_chunk);
+  const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
+  const size_t head_offset = (size_t)g * p.page_size * D + my_chunk * 8;
+  const size_t page_stride = (size_t)p.kv_heads * p.page_size * D;
+
+#pragma unroll 1
+  for (int pass = 0; pass < 2; ++pass) {
+  const int tile = pass == 0 ? q_tiles - 1 - (int)blockIdx.x : (int)blockIdx.x;
+  if (pass == 1 && tile == q_tiles - 1 - (int)blockIdx.x) break;      // the middle tile of an odd count
   const int rows = min(PREFILL_BQ, q_count - tile * PREFILL_BQ);
   const int pos0 = p.q_pos0[b] + tile * PREFILL_BQ;             // position of the block's first query
   const int kv_end = min(p.kv_len[b], pos0 + rows);
   const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int kv_begin = (first_key / TILE_KEYS) * TILE_KEYS;
-  const int g = h / (p.heads / p.kv_heads);
-  const int row_elems = (p.heads + 2 * p.kv_heads) * D;
-
-  const int warp_row0 = warp * 16;
   uint32_t q[D / 16][4];
   load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
     const int row = warp_row0 + r;
     return row < rows ? p.qkv + (size_t)(first_token + tile * PREFILL_BQ + row) * row_elems + (size_t)h * D : nullptr;
   });
 
-  constexpr int TILE_BYTES = PREFILL_BKEYS * D * 2;
-  const uint32_t smem_base = smem_u32(smem);
-  const int* table = p.block_table + (size_t)b * p.table_width;
-
   // All 128 threads bring a tile of 64 keys and values; keys past kv_end are zero-filled rows
-  // that the mask never lets through (their pages may not exist).
+  // that the mask never lets through (their pages may not exist). A thread copies the same
+  // 16-byte column of PER_THREAD rows in every tile, so where they go in shared memory is
+  // worked out once.
   auto fetch = [&](int stage, int key0) {
     const uint32_t k_dst = smem_base + stage * 2 * TILE_BYTES;
-    constexpr int CHUNKS = PREFILL_BKEYS * D / 8;
-#pragma unroll 2
-    for (int i = threadIdx.x; i < CHUNKS; i += 128) {
-      const int row = i / (D / 8), c = i % (D / 8);
-      const int key = key0 + row;
-      const int off = TileLayout<D>::offset_bytes(row, c);
+#pragma unroll
+    for (int j = 0; j < PER_THREAD; ++j) {
+      const int key = key0 + my_row + j * ROWS_PER_PASS;
       if (key < kv_end) {
-        const int page = table[key / p.page_size];
-        const size_t src = (((size_t)page * p.kv_heads + g) * p.page_size + (key % p.page_size)) * D + c * 8;
-        cp_async16(k_dst + off, p.keys + src);
-        cp_async16(k_dst + TILE_BYTES + off, p.values + src);
+        int page, offset;
+        if (page_shift >= 0) {
+          page = table[key >> page_shift];
+          offset = key & (p.page_size - 1);
+        } else {
+          page = table[key / p.page_size];
+          offset = key % p.page_size;
+        }
+        const size_t src = (size_t)page * page_stride + head_offset + (size_t)offset * D;
+        cp_async16(k_dst + dst_offset[j], p.keys + src);
+        cp_async16(k_dst + TILE_BYTES + dst_offset[j], p.values + src);
       } else {
-        *(uint4*)(smem + stage * 2 * TILE_BYTES + off) = make_uint4(0, 0, 0, 0);
-        *(uint4*)(smem + stage * 2 * TILE_BYTES + TILE_BYTES + off) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(smem + stage * 2 * TILE_BYTES + dst_offset[j]) = make_uint4(0, 0, 0, 0);
+        *(uint4*)(smem + stage * 2 * TILE_BYTES + TILE_BYTES + dst_offset[j]) = make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -469,7 +514,11 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
       float s[2][4];
       scores_16_keys<D>(s, q, k_tile, sub * 16);
       uint32_t pa[4];
-      softmax_step<D>(s, row_max, row_sum, o, pa, p.scale_log2, [&](int half, int key) {
+      // Keys wholly before the warp's first row, inside every row's window and inside the
+      // request need no mask.
+      const bool unmasked = key0 + 15 <= pos0 + warp_row0 && key0 + 16 <= kv_end &&
+                            (p.window <= 0 || warp_last_pos - key0 < p.window);
+      softmax_step<D>(s, row_max, row_sum, o, pa, p.scale_log2, unmasked, [&](int half, int key) {
         const int j = key0 + key;
         return j < kv_end && j <= my_pos[half] && (p.window <= 0 || my_pos[half] - j < p.window);
       });
@@ -489,6 +538,7 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
     for (int n = 0; n < D / 8; ++n)
       *(uint32_t*)(out + n * 8 + (lane & 3) * 2) = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
   }
+  }  // the block's two tiles
 }
 
 // Raises a kernel's dynamic shared memory limit, once per kernel and process.
@@ -522,7 +572,8 @@ template <int D>
 int launch_prefill(const PrefillParams& p, int seqs, int max_q_len, cudaStream_t s) {
   const size_t bytes = (size_t)2 * 2 * PREFILL_BKEYS * D * 2;
   if (int err = allow_smem(prefill_kernel<D>, bytes, "paged_attention_prefill")) return err;
-  dim3 grid((max_q_len + PREFILL_BQ - 1) / PREFILL_BQ, p.heads, seqs);
+  const int q_tiles = (max_q_len + PREFILL_BQ - 1) / PREFILL_BQ;
+  dim3 grid((q_tiles + 1) / 2, p.heads, seqs);
   launch_kernel(prefill_kernel<D>, grid, 128, bytes, s, p);
   return check_launch("paged_attention_prefill");
 }

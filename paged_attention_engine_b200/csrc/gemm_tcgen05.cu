@@ -167,6 +167,70 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// One thread's 16 consecutive outputs of row `row` from column `col0` on: bias, residual,
+// rounding, store (16-byte stores when the row pitch allows).
+__device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, float* v) {
+    const int valid = min(16, p.rows_b - col0);
+    if (p.bias != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (i < valid) v[i] += p.bias[col0 + i];
+    }
+    const size_t at = (size_t)row * p.ld_out + col0;
+    if (p.out_f32) {
+      float* out = (float*)p.out + at;
+      if (p.residual != nullptr) {
+        const float* res = (const float*)p.residual + at;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < valid) v[i] += res[i];
+      }
+      if (valid == 16 && (at & 3) == 0) {
+#pragma unroll
+        for (int i = 0; i < 16; i += 4) *(float4*)(out + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < valid) out[i] = v[i];
+      }
+    } else {
+      __nv_bfloat16* out = (__nv_bfloat16*)p.out + at;
+      if (p.residual != nullptr) {
+        const __nv_bfloat16* res = (const __nv_bfloat16*)p.residual + at;
+        if (valid == 16 && (at & 7) == 0) {
+          uint4 r0 = *(const uint4*)res, r1 = *(const uint4*)(res + 8);
+          const __nv_bfloat16* rr0 = (const __nv_bfloat16*)&r0;
+          const __nv_bfloat16* rr1 = (const __nv_bfloat16*)&r1;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] += __bfloat162float(rr0[i]);
+            v[8 + i] += __bfloat162float(rr1[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (i < valid) v[i] += __bfloat162float(res[i]);
+        }
+      }
+      if (valid == 16 && (at & 7) == 0) {
+        uint4 w0, w1;
+        __nv_bfloat162* h0 = (__nv_bfloat162*)&w0;
+        __nv_bfloat162* h1 = (__nv_bfloat162*)&w1;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+          h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+        }
+        *(uint4*)out = w0;
+        *(uint4*)(out + 8) = w1;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < valid) out[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+}
+
 template <int BN>
 struct Tile {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -292,65 +356,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           for (int i = 0; i < 16; ++i)
             if (col0 + i < p.rows_b) out[(size_t)(col0 + i) * p.ld_out + row] = v[i];
         } else {
-          const int valid = min(16, p.rows_b - col0);
-          if (p.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              if (i < valid) v[i] += p.bias[col0 + i];
-          }
-          const size_t at = (size_t)row * p.ld_out + col0;
-          if (p.out_f32) {
-            float* out = (float*)p.out + at;
-            if (p.residual != nullptr) {
-              const float* res = (const float*)p.residual + at;
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < valid) v[i] += res[i];
-            }
-            if (valid == 16 && (at & 3) == 0) {
-#pragma unroll
-              for (int i = 0; i < 16; i += 4) *(float4*)(out + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < valid) out[i] = v[i];
-            }
-          } else {
-            __nv_bfloat16* out = (__nv_bfloat16*)p.out + at;
-            if (p.residual != nullptr) {
-              const __nv_bfloat16* res = (const __nv_bfloat16*)p.residual + at;
-              if (valid == 16 && (at & 7) == 0) {
-                uint4 r0 = *(const uint4*)res, r1 = *(const uint4*)(res + 8);
-                const __nv_bfloat16* rr0 = (const __nv_bfloat16*)&r0;
-                const __nv_bfloat16* rr1 = (const __nv_bfloat16*)&r1;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  v[i] += __bfloat162float(rr0[i]);
-                  v[8 + i] += __bfloat162float(rr1[i]);
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                  if (i < valid) v[i] += __bfloat162float(res[i]);
-              }
-            }
-            if (valid == 16 && (at & 7) == 0) {
-              uint4 w0, w1;
-              __nv_bfloat162* h0 = (__nv_bfloat162*)&w0;
-              __nv_bfloat162* h1 = (__nv_bfloat162*)&w1;
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
-              }
-              *(uint4*)out = w0;
-              *(uint4*)(out + 8) = w1;
-            } else {
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                if (i < valid) out[i] = __float2bfloat16_rn(v[i]);
-            }
-          }
+          store_row_chunk(p, row, col0, v);
         }
       }
     }
@@ -361,6 +367,159 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, T::TMEM_COLUMNS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// The many-token product as a persistent kernel: one block per SM walks over 128 x 256
+// output tiles. Four 48 KB stages keep about a microsecond of loads in flight; the
+// accumulator is double-buffered in tensor memory (2 x 256 columns), so the epilogue of a
+// tile (tcgen05.ld, bias, residual, rounding, stores) runs while the MMAs of the next tile
+// are issued. Tiles that share a weight tile are neighbours in the walk, so a weight tile
+// is read from memory once and found in L2 by the other blocks.
+// ---------------------------------------------------------------------------------------
+template <int PBN>
+struct PTile {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = PBN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 6 ? 6 : 200 * 1024 / STAGE_BYTES;
+  static constexpr int ACC_COLUMNS = 256;       // the two accumulators lie 256 columns apart
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int PBN>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                          const __grid_constant__ CUtensorMap map_b,
+                                                                          const Params p, int tiles_a, int tiles_b) {
+  constexpr int PSTAGES = PTile<PBN>::STAGES;
+  constexpr int P_A_BYTES = PTile<PBN>::A_BYTES;
+  constexpr int P_STAGE_BYTES = PTile<PBN>::STAGE_BYTES;
+  constexpr int ACC = PTile<PBN>::ACC_COLUMNS;
+  dependent_launch_trigger();
+  extern __shared__ uint8_t raw_smem[];
+  const uint32_t raw = smem_u32(raw_smem);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* generic_base = raw_smem + (base - raw);
+  const uint32_t bars = base + PSTAGES * P_STAGE_BYTES;   // full[S], empty[S], tmem_full[2], tmem_empty[2]
+  volatile uint32_t* tmem_holder = (volatile uint32_t*)(generic_base + PSTAGES * P_STAGE_BYTES + 8 * (2 * PSTAGES + 4));
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (PSTAGES + s); };
+  auto tmem_full_bar = [&](int a) { return bars + 8u * (2 * PSTAGES + a); };
+  auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * PSTAGES + 2 + a); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PSTAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 128);       // every epilogue thread arrives
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_holder), 2 * ACC);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  dependent_launch_wait();
+
+  const int total_tiles = tiles_a * tiles_b;
+  const int k_blocks = p.k_blocks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;     // neighbours share the weight tile
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          if (it >= PSTAGES && !mbar_wait(empty_bar(s), ((it / PSTAGES) - 1) & 1, abort_flag, p.error, 1)) {
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = base + s * P_STAGE_BYTES;
+          mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, full_bar(s), kb * BK, tile_a * BM);
+          tma_load_2d(a_dst + P_A_BYTES, &map_b, full_bar(s), kb * BK, tile_b * PBN);
+        }
+      }
+      if (*abort_flag) {
+        for (int i = max(0, it - PSTAGES); i < it; ++i)
+          for (uint32_t t = 0; t < WAIT_LIMIT && !mbar_try_wait(full_bar(i % PSTAGES), (i / PSTAGES) & 1); ++t) __nanosleep(64);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instruction_descriptor(BM, PBN);
+      int it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        const int acc = local & 1, use = local >> 1;
+        if (local >= 2) ok = mbar_wait(tmem_empty_bar(acc), (use - 1) & 1, abort_flag, p.error, 4);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * ACC;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % PSTAGES;
+          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1, abort_flag, p.error, 2);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t a_addr = base + s * P_STAGE_BYTES;
+          const uint32_t b_addr = a_addr + P_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_acc, smem_descriptor(a_addr + k * UMMA_K * 2), smem_descriptor(b_addr + k * UMMA_K * 2), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          tcgen05_commit(empty_bar(s));
+        }
+        if (ok) tcgen05_commit(tmem_full_bar(acc));
+      }
+    }
+  } else {
+    const int quadrant = warp & 3;
+    const int row_in_tile = quadrant * 32 + lane;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+      const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
+      const int acc = local & 1, use = local >> 1;
+      ok = ok && mbar_wait(tmem_full_bar(acc), use & 1, abort_flag, p.error, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = tile_a * BM + row_in_tile;
+      const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
+#pragma unroll 1
+      for (int c0 = 0; c0 < PBN; c0 += 16) {
+        float v[16];
+        tmem_load16(lane_address + c0, v);
+        const int col0 = tile_b * PBN + c0;
+        if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v);
+      }
+      tcgen05_fence_before();
+      mbar_arrive(tmem_empty_bar(acc));        // this thread has read its lane of the accumulator
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 2 * ACC);
   }
 }
 
@@ -442,6 +601,53 @@ int launch(const Params& p, const void* a, const void* b, int k, int splits, cud
   return check_launch("linear_tcgen05");
 }
 
+int sm_count() {
+  static int count = [] {
+    int device = 0, n = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+    return n;
+  }();
+  return count;
+}
+
+template <int PBN>
+int launch_persistent_with(const Params& p, const void* a, const void* b, int k, cudaStream_t stream) {
+  using T = PTile<PBN>;
+  CUtensorMap map_a, map_b;
+  if (int err = tensor_map(&map_a, a, p.rows_a, k, BM)) return err;
+  if (int err = tensor_map(&map_b, b, p.rows_b, k, PBN)) return err;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<PBN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_BYTES);
+    if (err != cudaSuccess) return fail(100, "linear_tcgen05: %s", cudaGetErrorString(err));
+    configured = true;
+  }
+  const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + PBN - 1) / PBN;
+  const int blocks = tiles_a * tiles_b < sm_count() ? tiles_a * tiles_b : sm_count();
+  launch_kernel(gemm_tcgen05_persistent_kernel<PBN>, dim3(blocks), THREADS, T::SMEM_BYTES, stream, map_a, map_b, p, tiles_a, tiles_b);
+  return check_launch("linear_tcgen05");
+}
+
+// The tile width whose walk over the output costs least: rounds of tiles over the SMs
+// times (width + a fixed share for a tile's first loads and its epilogue).
+int launch_persistent(const Params& p, const void* a, const void* b, int k, cudaStream_t stream) {
+  const int widths[3] = {256, 192, 176};
+  const int tiles_a = (p.rows_a + BM - 1) / BM;
+  int best = 256;
+  long best_cost = -1;
+  for (int w : widths) {
+    const int tiles = tiles_a * ((p.rows_b + w - 1) / w);
+    const long cost = (long)((tiles + sm_count() - 1) / sm_count()) * (w + 32);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = w;
+    }
+  }
+  if (best == 192) return launch_persistent_with<192>(p, a, b, k, stream);
+  if (best == 176) return launch_persistent_with<176>(p, a, b, k, stream);
+  return launch_persistent_with<256>(p, a, b, k, stream);
+}
+
 int check_operands(const void* x, const void* w, int k) {
   if (k % 8) return fail(2, "linear_tcgen05: K = %d is not a multiple of 8 (a TMA row pitch must be a multiple of 16 bytes)", k);
   if (((uintptr_t)x | (uintptr_t)w) & 15) return fail(2, "linear_tcgen05: an operand does not start on a 16-byte boundary");
@@ -468,6 +674,7 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
   p.out_f32 = out_f32;
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
+  if (n >= 256) return launch_persistent(p, x, w, k, s);
   if (n >= 128) return launch<128, NORMAL>(p, x, w, k, 1, s);
   if (n > 32) return launch<64, NORMAL>(p, x, w, k, 1, s);
   return launch<32, NORMAL>(p, x, w, k, 1, s);
