@@ -210,7 +210,10 @@ def time_end_to_end(engine, batch: int, steps: int, warmup: int, torch):
     from paged_attention_engine_b200 import LLM, Request
     from paged_attention_engine_b200.kernels import ops
 
-    prompt_len = CONTEXT - (warmup + steps) - 1
+    # Prompts are cut into portions under the token budget, so requests start to decode a few
+    # steps apart; SLACK extra tokens keep every request alive through the timed steps.
+    SLACK = 8
+    prompt_len = CONTEXT - (warmup + steps) - SLACK - 1
     llm = LLM(
         engine, num_blocks=batch * (CONTEXT // BLOCK_SIZE + 1) + 8, block_size=BLOCK_SIZE,
         max_num_seqs=batch, max_num_batched_tokens=8192,
@@ -218,7 +221,7 @@ def time_end_to_end(engine, batch: int, steps: int, warmup: int, torch):
     gen = torch.Generator().manual_seed(7)
     for b in range(batch):
         prompt = torch.randint(0, engine.vocab_size, (prompt_len,), generator=gen).tolist()
-        assert llm.add_request(Request(f"e2e-{b}", tuple(prompt), warmup + steps + 1))
+        assert llm.add_request(Request(f"e2e-{b}", tuple(prompt), warmup + steps + SLACK + 1))
     while llm.scheduler.waiting or any(s.num_computed < s.request.prompt_len for s in llm.scheduler.running):
         llm.step()
     for _ in range(warmup):
@@ -230,12 +233,13 @@ def time_end_to_end(engine, batch: int, steps: int, warmup: int, torch):
     for _ in range(steps):
         result = llm.step()
         produced += len(result.decoded)
+    llm.scheduler.resolve()            # the last steps' tokens reach the host inside the timed region
     torch.cuda.synchronize()
     elapsed = time.perf_counter() - t0
+    assert all(min(s.generated) >= 0 for s in llm.scheduler.running)
     # Per step: the packed integer arrays of the batch (tokens, positions, starts, lengths,
     # slots, block tables) and the sampler's rows go to the device; the tokens come back.
-    width = CONTEXT // BLOCK_SIZE
-    h2d = 4 * (4 * batch + 4 * batch + batch * width + batch + 8) + 4 * 5 * batch
+    h2d = llm.runner.builder.bytes_uploaded      # the last step's copy: all steps of the region have this size
     d2h = 4 * batch
     return {
         "value": produced / elapsed, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -295,7 +299,6 @@ def main() -> int:
     sampler = ClockSampler()
     sampler.start()
     decode = time_decode(engine, args.batch, args.steps, warmup, torch, Sampler, SamplingRow)
-    clocks = sampler.stop()
 
     points = {}
     if not args.skip_points:
@@ -303,6 +306,7 @@ def main() -> int:
             points[name] = round(time_decode(engine, b, max(8, args.steps // 2), 3, torch, Sampler, SamplingRow)["tokens_per_s"], 1)
     prefill_ms = time_prefill(engine, torch)
     e2e = time_end_to_end(engine, args.batch, args.steps, warmup, torch)
+    clocks = sampler.stop()      # sampled through every timed region of this run
 
     flops = prefill_flops(model, PREFILL_TOKENS)
     achieved = decode["bytes"] / (decode["ms_per_step"] / 1e3) / 1e9

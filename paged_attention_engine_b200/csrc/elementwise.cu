@@ -39,6 +39,58 @@ PAE_EXPORT int pae_gather_rows(void* out, const void* table, const int* index, i
 }
 
 // ------------------------------------------------------------------------------------
+// Token embedding with feedback. A negative token id stands for "the token this request
+// sampled in the step before", which is still on the device: the kernel reads it from
+// last_token[state_slot[seq_index[t]]]. `scatter_tokens` is what puts it there after
+// sampling. Together they let the host plan the next step while this one runs; the
+// reference reads every sampled token back before it goes on (engine/scheduler.py:610).
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_feedback_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                                          const int* __restrict__ last_token, const int* __restrict__ state_slot,
+                                          const int* __restrict__ seq_index, int rows, int width) {
+  dependent_launch_prologue();
+  const int t = blockIdx.x;
+  int src = ids[t];
+  if (src < 0) src = last_token[state_slot[seq_index[t]]];
+  const bool ok = src >= 0 && src < rows;
+  const T* from = table + (size_t)(ok ? src : 0) * width;
+  T* to = out + (size_t)t * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) to[i] = ok ? from[i] : from_float<T>(0.f);
+}
+
+PAE_EXPORT int pae_embedding_feedback(void* out, const void* table, const int* ids, const int* last_token,
+                                      const int* state_slot, const int* seq_index, int n, int rows, int width, int dtype,
+                                      void* stream) {
+  if (n == 0) return 0;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : 64);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32)
+    launch_kernel(embedding_feedback_kernel<float>, n, threads, 0, s, (float*)out, (const float*)table, ids, last_token, state_slot, seq_index, rows, width);
+  else if (dtype == kBF16)
+    launch_kernel(embedding_feedback_kernel<__nv_bfloat16>, n, threads, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, last_token, state_slot, seq_index, rows, width);
+  else
+    return fail(1, "embedding_feedback: unknown dtype %d", dtype);
+  return check_launch("embedding_feedback");
+}
+
+// last_token[state_slot[seq_index[logit_rows[r]]]] = tokens[r] for every sampled row r.
+__global__ void scatter_tokens_kernel(int* __restrict__ last_token, const int* __restrict__ tokens,
+                                      const int* __restrict__ logit_rows, const int* __restrict__ seq_index,
+                                      const int* __restrict__ state_slot, int n) {
+  dependent_launch_prologue();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < n) last_token[state_slot[seq_index[logit_rows[r]]]] = tokens[r];
+}
+
+PAE_EXPORT int pae_scatter_tokens(int* last_token, const int* tokens, const int* logit_rows, const int* seq_index,
+                                  const int* state_slot, int n, void* stream) {
+  if (n == 0) return 0;
+  launch_kernel(scatter_tokens_kernel, (n + 127) / 128, 128, 0, (cudaStream_t)stream, last_token, tokens, logit_rows, seq_index, state_slot, n);
+  return check_launch("scatter_tokens");
+}
+
+// ------------------------------------------------------------------------------------
 // RMSNorm (engine/model.py:117-123): y = w * x * rsqrt(mean(x^2) + eps), statistics and
 // scaling in float32, weight in float32, one rounding at the end. One block per row;
 // the order of the sum depends on the width only, never on the batch.

@@ -33,12 +33,13 @@ class LLM:
         admission_margin_blocks: int = ADMISSION_MARGIN_BLOCKS,
         record_logits: bool = False,
         use_graphs: bool = True,
+        asynchronous: bool | None = None,
     ) -> None:
         self.engine = engine
         slots = max_num_seqs if max_num_seqs is not None else 256
         self.cache = engine.new_paged_cache(num_blocks, block_size, slots)
         self.runner = engine.new_runner(self.cache, use_graphs)
-        self.executor = ModelExecutor(self.runner)
+        self.executor = ModelExecutor(self.runner, asynchronous)
         self.scheduler = Scheduler(
             self.executor, self.cache.manager, admission_margin_blocks=admission_margin_blocks,
             record_logits=record_logits, max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,

@@ -64,6 +64,8 @@ class StepContext:
     # (temperature, seed_lo, seed_hi, request_key, output_index), one element per wanted place
     sampling: tuple | None = None
     buffer: torch.Tensor | None = None    # the one device tensor that all integer arrays above are views of
+    # (last_token [slots], state_slot, seq_index): where a token id of -1 is looked up on the device
+    feedback: tuple | None = None
     memo: dict = field(default_factory=dict)
 
 
@@ -191,8 +193,9 @@ class BatchBuilder:
             seq_index = np.repeat(np.arange(b, dtype=np.int32), q_lens)
             positions = np.concatenate([np.arange(p, p + n, dtype=np.int32) for p, n in zip(pos0, q_lens)])
             kv_len = pos0_arr + np.asarray(q_lens, dtype=np.int32)
-        if self.vocab_size is not None and (int(token_ids.min()) < 0 or int(token_ids.max()) >= self.vocab_size):
-            bad = int(token_ids[(token_ids < 0) | (token_ids >= self.vocab_size)][0])
+        # -1 is not a token: it asks for the token the request sampled in the step before.
+        if self.vocab_size is not None and (int(token_ids.min()) < -1 or int(token_ids.max()) >= self.vocab_size):
+            bad = int(token_ids[(token_ids < -1) | (token_ids >= self.vocab_size)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
         rows = [int(q_start[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
 

@@ -15,11 +15,36 @@ from .runner import ModelRunner
 from .scheduler import ScheduledWork, WorkResult
 
 
+class _TokenFuture:
+    """Sampled tokens on their way to the host: a copy into pinned memory and an event."""
+
+    def __init__(self, tokens: torch.Tensor, host: torch.Tensor) -> None:
+        self.host = host[: tokens.numel()]
+        self.host.copy_(tokens, non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record()
+        self.values: list[int] | None = None
+
+    def result(self) -> list[int]:
+        if self.values is None:
+            self.event.synchronize()
+            self.values = self.host.tolist()
+        return self.values
+
+
 class ModelExecutor:
-    def __init__(self, runner: ModelRunner) -> None:
+    """`asynchronous` (the default on a GPU): `execute` returns as soon as the step is queued;
+    sampled tokens stay on the device, feed the next step there, and reach the host a step
+    later through a `_TokenFuture`. With `record_logits` the step is read back at once."""
+
+    def __init__(self, runner: ModelRunner, asynchronous: bool | None = None) -> None:
         self.runner = runner
         self.manager = runner.manager
         self.sampler = Sampler(runner.runtime.ops, runner.runtime.device)
+        on_gpu = runner.runtime.device.type == "cuda"
+        self.asynchronous = on_gpu if asynchronous is None else (asynchronous and on_gpu)
+        self._host_tokens = [torch.empty(1024, dtype=torch.int32).pin_memory() for _ in range(4)] if on_gpu else []
+        self._turn = 0
 
     def begin(self, key: Hashable) -> bool:
         return self.runner.begin_request(key)
@@ -46,7 +71,15 @@ class ModelExecutor:
                 )
         output = self.runner.step(entries, rows if rows else None)
         results = [WorkResult(None) for _ in work]
-        if rows:
+        if rows and self.asynchronous and not record_logits and len(rows) <= 1024:
+            future = _TokenFuture(output.tokens, self._host_tokens[self._turn])
+            self._turn = (self._turn + 1) % len(self._host_tokens)
+            at = 0
+            for i, w in enumerate(work):
+                if w.wants_token:
+                    results[i] = WorkResult(None, None, future, at)
+                    at += 1
+        elif rows:
             tokens = output.tokens.cpu().tolist()
             logits = output.logits.float().cpu() if record_logits else None
             at = 0

@@ -62,6 +62,9 @@ class ModelRunner:
         self.use_graphs = use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
         self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self.graph_replays = 0
+        # The token last sampled for the request in each state slot; a step's token id of -1
+        # reads it, so a sampled token can feed the next step without a trip to the host.
+        self.last_token = torch.zeros(self.manager.slots.num_slots, dtype=torch.int32, device=self.runtime.device)
 
     def begin_request(self, key: Hashable) -> bool:
         """Registers a request (state slot, empty block tables); False when no slot is free."""
@@ -77,10 +80,13 @@ class ModelRunner:
     # ------------------------------------------------------------------ #
 
     def _run(self, ctx):
+        ctx.feedback = (self.last_token, ctx.state_slot, ctx.seq_index)
         logits = self.model.forward(ctx, self.entry_caches)
         tokens = None
         if ctx.sampling is not None and logits is not None:
-            tokens = self.runtime.ops.sample(logits, *ctx.sampling)
+            ops = self.runtime.ops
+            tokens = ops.sample(logits, *ctx.sampling)
+            ops.scatter_tokens(self.last_token, tokens, ctx.logit_rows, ctx.seq_index, ctx.state_slot)
         return logits, tokens
 
     def _graph_key(self, entries, sampling) -> tuple[int, int, bool] | None:

@@ -180,10 +180,22 @@ class StepResult:
     prefilled: tuple[str, ...] = ()        # requests that ran a portion of their history
 
 
+# What stands in `Sequence.generated` for a token that was sampled on the device and has
+# not been read back yet. It is also what the step function takes for "the token this
+# request sampled in the step before".
+PENDING = -1
+
+
 @dataclass
 class WorkResult:
+    """The token of one portion, or a `future` whose `result()[row]` will be that token: an
+    executor may leave sampled tokens on the device and hand them over a step later, so that
+    the host plans the next step while this one runs."""
+
     token: int | None
     logits: object = None
+    future: object = None
+    row: int = -1
 
 
 class Executor(Protocol):
@@ -210,6 +222,7 @@ class Scheduler:
         max_num_seqs: int | None = None,
         max_num_batched_tokens: int | None = None,
         max_model_len: int | None = None,
+        pipeline_depth: int = 2,
     ) -> None:
         if admission_margin_blocks < 0:
             raise ValueError(f"admission_margin_blocks must not be negative, got {admission_margin_blocks}")
@@ -225,6 +238,9 @@ class Scheduler:
         self.max_num_seqs = max_num_seqs
         self.max_num_batched_tokens = max_num_batched_tokens
         self.max_model_len = max_model_len
+        # How many steps may be under way before the oldest one's tokens are read back (only
+        # an executor that hands out futures makes use of it).
+        self.pipeline_depth = max(1, pipeline_depth)
 
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
@@ -235,6 +251,7 @@ class Scheduler:
         self._next_arrival = 0
         self._plan: list[ScheduledWork] = []
         self._budget_left = 0
+        self._unresolved: list[tuple[Sequence, int, object, int]] = []   # (sequence, index in generated, future, row)
 
     # -- log ---------------------------------------------------------------- #
 
@@ -305,8 +322,26 @@ class Scheduler:
             admitted.append(head)
         return admitted
 
+    def resolve(self, keep_steps: int = 0) -> None:
+        """Reads back the sampled tokens that are still on the device, all but those of the
+        newest `keep_steps` steps (waits for the steps it reads)."""
+        futures = []
+        for _, _, future, _ in self._unresolved:
+            if not futures or futures[-1] is not future:
+                futures.append(future)
+        keep = set(id(f) for f in futures[len(futures) - keep_steps:]) if keep_steps > 0 else set()
+        left = []
+        for seq, index, future, row in self._unresolved:
+            if id(future) in keep:
+                left.append((seq, index, future, row))
+            else:
+                seq.generated[index] = int(future.result()[row])
+        self._unresolved = left
+
     def _start(self, seq: Sequence) -> None:
         is_recompute = bool(seq.generated)
+        if is_recompute and seq.generated[-1] == PENDING:
+            self.resolve()        # a recompute replays the tokens themselves
         if not self.executor.begin(seq.request_id):
             raise AssertionError(f"{seq.request_id}: no state slot although the capacity check passed")
         seq.status = SequenceStatus.RUNNING
@@ -430,16 +465,23 @@ class Scheduler:
         results = self.executor.execute(plan, self.record_logits)
         if len(results) != len(plan):
             raise AssertionError(f"the executor answered {len(results)} results for {len(plan)} portions")
+        # This step is on its way; the tokens of older steps can be read now without leaving
+        # the device idle (this step's own futures are appended below).
+        self.resolve(keep_steps=self.pipeline_depth - 1)
         for work, result in zip(plan, results):
             seq = work.seq
             seq.num_computed += len(work.token_ids)
             if not work.wants_token:
                 continue
-            if result.token is None:
-                raise AssertionError(f"{seq.request_id}: no token for a portion that ended its history")
             if self.record_logits:
                 seq.step_logits.append(result.logits)
-            seq.generated.append(int(result.token))
+            if result.future is not None:
+                seq.generated.append(PENDING)
+                self._unresolved.append((seq, len(seq.generated) - 1, result.future, result.row))
+            elif result.token is None:
+                raise AssertionError(f"{seq.request_id}: no token for a portion that ended its history")
+            else:
+                seq.generated.append(int(result.token))
             if seq.is_finished:
                 self._finish(seq)
         return plan
@@ -463,4 +505,5 @@ class Scheduler:
                 raise RuntimeError(
                     f"no progress after {max_steps} steps: {len(self.waiting)} waiting, {len(self.running)} running"
                 )
+        self.resolve()
         return {rid: tuple(seq.generated) for rid, seq in self.finished.items()}

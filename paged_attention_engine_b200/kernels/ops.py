@@ -145,8 +145,33 @@ def gather_rows(x, rows: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
-    return gather_rows(table, ids)
+def embedding(ids: torch.Tensor, table: torch.Tensor, feedback=None) -> torch.Tensor:
+    """Rows of `table` for the token ids. With `feedback` = (last_token, state_slot, seq_index) a
+    negative id stands for the token that the request sampled in the step before, read from
+    last_token[state_slot[seq_index[t]]] on the device."""
+    if feedback is None:
+        return gather_rows(table, ids)
+    last_token, state_slot, seq_index = feedback
+    _need(table, "embedding: table")
+    for name, t in (("ids", ids), ("last_token", last_token), ("state_slot", state_slot), ("seq_index", seq_index)):
+        _need(t, f"embedding: {name}", torch.int32)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_embedding_feedback(_ptr(out), _ptr(table), _ptr(ids), _ptr(last_token), _ptr(state_slot),
+                                           _ptr(seq_index), c_int(ids.numel()), c_int(table.shape[0]),
+                                           c_int(table.shape[1]), c_int(_code(table)), _stream()))
+    return out
+
+
+def scatter_tokens(last_token, tokens, logit_rows, seq_index, state_slot) -> None:
+    """last_token[state_slot[seq_index[logit_rows[r]]]] = tokens[r]: the sampled tokens stay on the
+    device where the next step's embedding finds them."""
+    for name, t in (("last_token", last_token), ("tokens", tokens), ("logit_rows", logit_rows),
+                    ("seq_index", seq_index), ("state_slot", state_slot)):
+        _need(t, f"scatter_tokens: {name}", torch.int32)
+    lib = _lib("elementwise")
+    _check(lib, lib.pae_scatter_tokens(_ptr(last_token), _ptr(tokens), _ptr(logit_rows), _ptr(seq_index),
+                                       _ptr(state_slot), c_int(tokens.numel()), _stream()))
 
 
 def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:

@@ -24,7 +24,9 @@ class TokenEmbedding(Part):
         self.weight = tensors[spec.tensor_name("weight")]
 
     def forward(self, ctx):
-        return self.ops.embedding(ctx.token_ids, self.weight)
+        # A negative id is "the token sampled for this request in the step before" (see
+        # StepContext.feedback); the kernel looks it up on the device.
+        return self.ops.embedding(ctx.token_ids, self.weight, getattr(ctx, "feedback", None))
 
 
 @HEADS.register("lm_head")

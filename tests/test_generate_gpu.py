@@ -112,3 +112,29 @@ def test_preemption_and_recompute_on_the_gpu(tmp_path_factory, dtype_name):
         _teacher_forced_check(folder, DTYPES[dtype_name], prompt, tight[rid], llm.scheduler.finished[rid].step_logits)
     if dtype_name == "float32":
         assert tight == roomy
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_tokens_fed_forward_on_the_device_equal_tokens_read_back(tmp_path_factory, dtype_name, temperature):
+    """The asynchronous executor leaves sampled tokens on the device, feeds them to the next step
+    there and reads them a step later; the synchronous one reads each step's tokens before it
+    plans the next. Same requests, same pool (small enough to preempt), same tokens."""
+    from paged_attention_engine_b200 import LLM, EventKind, Request
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_b", dtype_name)
+    prompts = {f"a{i}": tuple(helpers.random_tokens(raw["vocab_size"], n, 600 + n)) for i, n in enumerate((20, 31, 1, 12, 40, 5))}
+
+    def run(asynchronous):
+        llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=9, block_size=page, max_num_seqs=4,
+                                  max_num_batched_tokens=48, asynchronous=asynchronous)
+        for rid, prompt in prompts.items():
+            assert llm.add_request(Request(rid, prompt, 30, temperature=temperature, seed=5))
+        out = llm.run_to_completion()
+        return out, llm
+
+    late, llm = run(True)
+    assert llm.executor.asynchronous and llm.scheduler.events_of(EventKind.PREEMPT)
+    now, _ = run(False)
+    assert late == now
+    assert all(len(v) == 30 and min(v) >= 0 for v in late.values())

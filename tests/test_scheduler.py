@@ -12,7 +12,7 @@ from stub_executor import StubExecutor, expected_tokens, make_manager
 
 def build(num_blocks, block_size=4, **options):
     manager = make_manager(num_blocks, block_size, window=options.pop("window", 0))
-    executor = StubExecutor(manager)
+    executor = StubExecutor(manager, deferred=options.pop("deferred", False))
     clock = iter(range(10**9))
     return Scheduler(executor, manager, clock=lambda: float(next(clock)), **options), executor, manager
 
@@ -247,3 +247,26 @@ def test_event_log_records_capacity_and_occupancy():
     sched.run_to_completion()
     finish = sched.events_of(EventKind.FINISH)[0]
     assert finish.free_blocks == 10 and finish.tokens_held == 0 and "2 tokens" in finish.detail
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_tokens_that_arrive_a_step_late_change_nothing(seed):
+    """An executor may hand over sampled tokens a step later (they stay on the device and feed
+    the next step there). Decisions depend on counts only, so the same requests finish with
+    the same tokens; a recompute, which replays the tokens themselves, reads them first."""
+    rng = random.Random(200 + seed)
+    reqs = requests(rng, 20, 30, 25)
+    sched, executor, manager = build(rng.randint(8, 14), block_size=4, deferred=True,
+                                     max_num_batched_tokens=rng.choice([None, 9, 40]))
+    accepted = [r for r in reqs if sched.add_request(r)]
+    steps = 0
+    while sched.waiting or sched.running:
+        sched.step()
+        steps += 1
+        for seq in sched.running:
+            assert all(t >= 0 for t in seq.generated[:-sched.pipeline_depth]), "only the newest tokens may still be on their way"
+    out = sched.run_to_completion()
+    assert sched.events_of(EventKind.PREEMPT), "the pool is small enough to force a recompute"
+    for r in accepted:
+        assert out[r.request_id] == expected_tokens(r.prompt_token_ids, r.max_new_tokens)
+    check_all_returned(manager)

@@ -18,8 +18,17 @@ def materialized(x):
     return x
 
 
-def embedding(ids, table):
-    return table[ids.long()]
+def embedding(ids, table, feedback=None):
+    ids = ids.long()
+    if feedback is not None:
+        last_token, state_slot, seq_index = feedback
+        fed = last_token[state_slot[seq_index.long()].long()].long()
+        ids = torch.where(ids < 0, fed, ids)
+    return table[ids]
+
+
+def scatter_tokens(last_token, tokens, logit_rows, seq_index, state_slot):
+    last_token[state_slot[seq_index[logit_rows.long()].long()].long()] = tokens.to(last_token.dtype)
 
 
 def rms_norm(x, weight, eps):
