@@ -38,6 +38,7 @@ FAMILIES: dict[str, list[str]] = {
     "gemm_tcgen05": ["gemm_tcgen05.cu", "common.cuh"],
     "attention_mma": ["attention_mma.cu", "attention_mma.cuh", "common.cuh"],
     "fused_decode": ["fused_decode.cu", "common.cuh"],
+    "attention_tcgen05": ["attention_tcgen05.cu", "common.cuh"],
     "attention_decode_noalloc": [
         "attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_mma.cuh", "common.cuh",
     ],

@@ -346,6 +346,23 @@ def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int) -> tuple[int, int]
     return slice_keys, max_slices
 
 
+use_tcgen05_attention = True
+TCGEN05_ATTENTION_MIN_TOKENS = 64
+
+
+def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
+                      num_kv_heads, head_dim, page_size, max_kv_len, scale, window) -> None:
+    """The requests that bring one token: sliced over their keys, then merged."""
+    slice_keys, max_slices = decode_slicing(seqs if singles < 0 else singles, num_kv_heads, max_kv_len)
+    floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
+    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+    _check(lib, lib.pae_paged_attention_decode(
+        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_float(scale), c_int(window), c_int(slice_keys), c_int(max_slices),
+        _ptr(scratch), _stream()), 2)
+
+
 def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
                     page_size, max_q_len, max_kv_len, scale, window, num_single=None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages. `num_single` is the number
@@ -362,8 +379,24 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if qkv.dtype == torch.bfloat16 and use_tensor_cores:
         lib = _lib("attention_mma")
-        if lib.pae_attention_mma_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
-            singles = num_single if num_single is not None else (seqs if max_q_len == 1 else -1)
+        mma_ok = bool(lib.pae_attention_mma_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)))
+        singles = num_single if num_single is not None else (seqs if max_q_len == 1 else -1)
+        # Portions of 64 tokens and more: both products on tcgen05, one thread per query row.
+        if use_tcgen05_attention and max_q_len >= TCGEN05_ATTENTION_MIN_TOKENS:
+            tc5 = _lib("attention_tcgen05")
+            if tc5.pae_attention_tcgen05_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
+                decode_after = mma_ok and singles != 0
+                _check(tc5, tc5.pae_paged_attention_prefill_tcgen05(
+                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), ctypes.c_longlong(keys.shape[0]), _ptr(block_table),
+                    c_int(block_table.shape[1]), _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(tokens), c_int(seqs),
+                    c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), _ptr(_error_flag(qkv.device)),
+                    _stream()))
+                if decode_after:
+                    _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles,
+                                      num_heads, num_kv_heads, head_dim, page_size, max_kv_len, scale, window)
+                return out
+        if mma_ok:
             if max_q_len > 1:
                 _check(lib, lib.pae_paged_attention_prefill(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
@@ -371,14 +404,8 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
                     c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
                     c_int(1), _stream()))
             if singles != 0:
-                slice_keys, max_slices = decode_slicing(seqs if singles < 0 else singles, num_kv_heads, max_kv_len)
-                floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
-                scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
-                _check(lib, lib.pae_paged_attention_decode(
-                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
-                    _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-                    c_int(page_size), c_float(scale), c_int(window), c_int(slice_keys), c_int(max_slices),
-                    _ptr(scratch), _stream()), 2)
+                _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
+                                  num_kv_heads, head_dim, page_size, max_kv_len, scale, window)
             return out
     lib = _lib("attention_simt")
     _check(lib, lib.pae_paged_attention_simt(

@@ -250,3 +250,28 @@ def test_tensor_core_attention_agrees_with_the_cuda_core_kernel(ops):
     finally:
         ops.use_tensor_cores = True
     assert (fast.float() - slow.float()).abs().max().item() <= 2.0 ** -6 * float(slow.float().abs().max())
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [
+    (12, 2, 128, 16, 0), (4, 4, 64, 16, 0), (3, 1, 128, 32, 0), (6, 3, 128, 16, 100), (2, 1, 64, 64, 17), (5, 5, 128, 128, 0),
+])
+def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window):
+    """The tcgen05 form: portions of 64 tokens and more at offsets that are ragged against its
+    128-row tiles, the pages and the 128-key tiles, beside shorter portions and single tokens."""
+    gen = torch.Generator().manual_seed(31)
+    q_lens = [300, 1, 129, 2, 128, 1, 65, 700]
+    pos0 = [0, 500, 1000, 31, 64, 0, 77, 5]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
+    want = ref.paged_attention(*tensors, **args)
+    assert ops.use_tcgen05_attention
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    ops.check_device_errors()
+    _close(got, want, torch.bfloat16, scale=2.0)
+    ops.use_tcgen05_attention = False
+    try:
+        other = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    finally:
+        ops.use_tcgen05_attention = True
+    assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -6 * float(other.float().abs().max())
