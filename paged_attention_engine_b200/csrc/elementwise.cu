@@ -294,14 +294,17 @@ PAE_EXPORT int pae_rotary_qk_cache_write(void* qkv, const float* table, const in
 // where a row of the input holds the gate in [0, I) and the up projection in [I, 2I).
 // ------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, long long total, int inter) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gate_up, long long total, int inter, int block) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long t = i / inter;
   const int c = (int)(i - t * inter);
-  const float g = to_float(gate_up[t * 2 * inter + c]);
-  const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+  // block 0: gate in columns [0, I), up in [I, 2I); block b > 0: b gate columns, b up columns, and so on.
+  const int gate_col = block > 0 ? (c / block) * 2 * block + c % block : c;
+  const int up_col = block > 0 ? gate_col + block : inter + c;
+  const float g = to_float(gate_up[t * 2 * inter + gate_col]);
+  const float u = to_float(gate_up[t * 2 * inter + up_col]);
   out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
@@ -328,10 +331,10 @@ __global__ void silu_mul_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
   *(uint4*)(out + t * inter + c * 8) = packed;
 }
 
-PAE_EXPORT int pae_silu_mul(void* out, const void* gate_up, int tokens, int inter, int dtype, void* stream) {
+PAE_EXPORT int pae_silu_mul(void* out, const void* gate_up, int tokens, int inter, int block, int dtype, void* stream) {
   const long long n = (long long)tokens * inter;
   if (n == 0) return 0;
-  if (dtype == kBF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+  if (block == 0 && dtype == kBF16 && inter % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     const long long chunks = n / 8;
     launch_kernel(silu_mul_bf16x8_kernel, (unsigned)((chunks + 255) / 256), 256, 0, (cudaStream_t)stream, 
         (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, chunks, inter);
@@ -340,9 +343,9 @@ PAE_EXPORT int pae_silu_mul(void* out, const void* gate_up, int tokens, int inte
   const unsigned blocks = (unsigned)((n + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32)
-    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, n, inter);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, (const float*)gate_up, n, inter, block);
   else if (dtype == kBF16)
-    launch_kernel(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, inter);
+    launch_kernel(silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, n, inter, block);
   else
     return fail(1, "silu_mul: unknown dtype %d", dtype);
   return check_launch("silu_mul");

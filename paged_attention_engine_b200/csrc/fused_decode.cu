@@ -128,15 +128,18 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
 // out[t, i] = silu(g) * u with g, u the rounded sums of columns i and inter + i.
 template <typename T>
 __global__ void splitk_silu_mul_kernel(T* __restrict__ out, const float* __restrict__ partial, int splits, int tokens,
-                                       int inter) {
+                                       int inter, int block) {
   dependent_launch_prologue();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)tokens * inter) return;
   const long long t = i / inter;
   const int c = (int)(i - t * inter);
   const size_t plane = (size_t)tokens * 2 * inter;
-  const float g = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + c)));
-  const float u = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + inter + c)));
+  // block 0: gate in columns [0, I), up in [I, 2I); block b > 0: b gate columns, b up columns, and so on.
+  const int gate_col = block > 0 ? (c / block) * 2 * block + c % block : c;
+  const int up_col = block > 0 ? gate_col + block : inter + c;
+  const float g = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + gate_col)));
+  const float u = to_float(from_float<T>(split_sum(partial, splits, plane, (size_t)t * 2 * inter + up_col)));
   out[i] = from_float<T>(g / (1.f + expf(-g)) * u);
 }
 
@@ -214,16 +217,16 @@ PAE_EXPORT int pae_splitk_rms_norm(void* normed, void* value, const float* parti
   return check_launch("splitk_rms_norm");
 }
 
-PAE_EXPORT int pae_splitk_silu_mul(void* out, const float* partial, int splits, int tokens, int inter, int dtype,
-                                   void* stream) {
+PAE_EXPORT int pae_splitk_silu_mul(void* out, const float* partial, int splits, int tokens, int inter, int block,
+                                   int dtype, void* stream) {
   const long long n = (long long)tokens * inter;
   if (n == 0) return 0;
   const unsigned blocks = (unsigned)((n + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kBF16)
-    launch_kernel(splitk_silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, splits, tokens, inter);
+    launch_kernel(splitk_silu_mul_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)out, partial, splits, tokens, inter, block);
   else if (dtype == kF32)
-    launch_kernel(splitk_silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, partial, splits, tokens, inter);
+    launch_kernel(splitk_silu_mul_kernel<float>, blocks, 256, 0, s, (float*)out, partial, splits, tokens, inter, block);
   else
     return fail(1, "splitk_silu_mul: unknown dtype %d", dtype);
   return check_launch("splitk_silu_mul");

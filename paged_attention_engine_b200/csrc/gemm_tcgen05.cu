@@ -52,6 +52,7 @@ struct Params {
   int kb_per_split;
   int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
   int out_f32;
+  int swiglu;        // NORMAL only: columns come in blocks of 16 gate, 16 up; out[row, n / 2] = silu(gate) * up
   int* error;
 };
 
@@ -229,6 +230,29 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int co
           if (i < valid) out[i] = __float2bfloat16_rn(v[i]);
       }
     }
+}
+
+// SwiGLU in the epilogue: 16 gate columns and the 16 up columns that follow them give 16
+// outputs. Gate and up are rounded to bfloat16 first, as the unfused path stores them.
+__device__ __forceinline__ void store_swiglu_chunk(const Params& p, int row, int col0, const float* g, const float* u) {
+  __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out + (col0 >> 1);
+  uint4 w0, w1;
+  __nv_bfloat162* h0 = (__nv_bfloat162*)&w0;
+  __nv_bfloat162* h1 = (__nv_bfloat162*)&w1;
+  float r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float gg = __bfloat162float(__float2bfloat16_rn(g[i]));
+    const float uu = __bfloat162float(__float2bfloat16_rn(u[i]));
+    r[i] = gg / (1.f + expf(-gg)) * uu;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    h0[i] = __floats2bfloat162_rn(r[2 * i], r[2 * i + 1]);
+    h1[i] = __floats2bfloat162_rn(r[8 + 2 * i], r[8 + 2 * i + 1]);
+  }
+  *(uint4*)out = w0;
+  *(uint4*)(out + 8) = w1;
 }
 
 template <int BN>
@@ -503,12 +527,23 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
       tcgen05_fence_after();
       const int row = tile_a * BM + row_in_tile;
       const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
+      if (p.swiglu) {
 #pragma unroll 1
-      for (int c0 = 0; c0 < PBN; c0 += 16) {
-        float v[16];
-        tmem_load16(lane_address + c0, v);
-        const int col0 = tile_b * PBN + c0;
-        if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v);
+        for (int c0 = 0; c0 < PBN; c0 += 32) {
+          float gate[16], up[16];
+          tmem_load16(lane_address + c0, gate);
+          tmem_load16(lane_address + c0 + 16, up);
+          const int col0 = tile_b * PBN + c0;
+          if (row < p.rows_a && col0 < p.rows_b) store_swiglu_chunk(p, row, col0, gate, up);
+        }
+      } else {
+#pragma unroll 1
+        for (int c0 = 0; c0 < PBN; c0 += 16) {
+          float v[16];
+          tmem_load16(lane_address + c0, v);
+          const int col0 = tile_b * PBN + c0;
+          if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v);
+        }
       }
       tcgen05_fence_before();
       mbar_arrive(tmem_empty_bar(acc));        // this thread has read its lane of the accumulator
@@ -636,6 +671,7 @@ int launch_persistent(const Params& p, const void* a, const void* b, int k, cuda
   int best = 256;
   long best_cost = -1;
   for (int w : widths) {
+    if (p.swiglu && w % 32) continue;         // a tile must not cut a gate block from its up block
     const int tiles = tiles_a * ((p.rows_b + w - 1) / w);
     const long cost = (long)((tiles + sm_count() - 1) / sm_count()) * (w + 32);
     if (best_cost < 0 || cost < best_cost) {
@@ -658,6 +694,26 @@ int check_operands(const void* x, const void* w, int k) {
 
 // out[tokens, n] = x[tokens, k] . w[n, k]^T (+ bias[n]) (+ residual[tokens, n]); x, w, residual
 // bfloat16, bias float32, out bfloat16 or float32 (then residual is float32 too).
+// out[tokens, n / 2] = silu(gate) * up where x . w^T gives gate and up in alternating blocks of 16
+// columns (w's rows are laid out that way); many tokens only (the persistent kernel). n is a
+// multiple of 32 and at least 256.
+PAE_EXPORT int pae_linear_swiglu_tcgen05(void* out, const void* x, const void* w, int tokens, int n, int k, int* error,
+                                         void* stream) {
+  if (tokens == 0 || n == 0) return 0;
+  if (n % 32 || n < 256) return fail(2, "linear_swiglu_tcgen05: %d columns are not a multiple of 32 of at least 256", n);
+  if (int err = check_operands(x, w, k)) return err;
+  Params p{};
+  p.out = out;
+  p.rows_a = tokens;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = p.k_blocks;
+  p.ld_out = n / 2;
+  p.swiglu = 1;
+  p.error = error;
+  return launch_persistent(p, x, w, k, (cudaStream_t)stream);
+}
+
 PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const float* bias, const void* residual,
                                   int tokens, int n, int k, int out_f32, int* error, void* stream) {
   if (tokens == 0 || n == 0) return 0;

@@ -415,23 +415,60 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     return out
 
 
-def silu_mul(gate_up) -> torch.Tensor:
+def silu_mul(gate_up, block: int = 0) -> torch.Tensor:
+    """silu(gate) * up of a [tokens, 2 I] product. block 0: gate is columns [0, I) and up [I, 2 I);
+    block b: b gate columns, then their b up columns, and so on (`linear_swiglu`'s weight layout)."""
     tokens, two_i = gate_up.shape
-    if two_i % 2:
-        raise KernelError(f"silu_mul: rows of {two_i} do not split into gate and up")
+    if two_i % 2 or (block and two_i % (2 * block)):
+        raise KernelError(f"silu_mul: rows of {two_i} do not split into gate and up (blocks of {block})")
     if isinstance(gate_up, PendingSum) and gate_up.value is None and gate_up.bias is None and gate_up.residual is None:
         splits = gate_up.partial.shape[0]
         out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
         lib = _lib("fused_decode")
         _check(lib, lib.pae_splitk_silu_mul(_ptr(out), _ptr(gate_up.partial), c_int(splits), c_int(tokens),
-                                            c_int(two_i // 2), c_int(_DTYPE_CODE[gate_up.dtype]), _stream()))
+                                            c_int(two_i // 2), c_int(block), c_int(_DTYPE_CODE[gate_up.dtype]), _stream()))
         return out
     gate_up = materialized(gate_up)
     _need(gate_up, "silu_mul: gate_up")
     out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("elementwise")
-    _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), c_int(tokens), c_int(two_i // 2), c_int(_code(gate_up)), _stream()))
+    _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), c_int(tokens), c_int(two_i // 2), c_int(block),
+                                 c_int(_code(gate_up)), _stream()))
     return out
+
+
+SWIGLU_BLOCK = 16
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor | None:
+    """[2 I, K] with 16 gate rows, their 16 up rows, and so on: the weight layout of
+    `linear_swiglu`, in which a product's tile holds gate and up of the same columns. None
+    when I is not a multiple of 16."""
+    inter, k = gate.shape
+    if inter % SWIGLU_BLOCK:
+        return None
+    both = torch.stack((gate.view(inter // SWIGLU_BLOCK, SWIGLU_BLOCK, k), up.view(inter // SWIGLU_BLOCK, SWIGLU_BLOCK, k)), dim=1)
+    return both.reshape(2 * inter, k).contiguous()
+
+
+def linear_swiglu(x, weight) -> torch.Tensor:
+    """silu(x . Wg^T) * (x . Wu^T) -> [M, I] for a weight from `interleave_gate_up`. With many
+    tokens the activation runs in the product's epilogue; with few, in the kernel that sums the
+    splits; otherwise as a kernel of its own. Gate and up are rounded to the engine dtype first in
+    every one of them, so all give the same bits."""
+    x = materialized(x)
+    m, k = x.shape
+    n = weight.shape[0]
+    if (m > SWAPPED_MAX_TOKENS and n >= 256 and n % 32 == 0 and _tensor_core_shape(x, weight, None, x.dtype)
+            and weight.shape[1] == k):
+        _need(x, "linear_swiglu: x")
+        _need(weight, "linear_swiglu: weight")
+        out = torch.empty((m, n // 2), dtype=x.dtype, device=x.device)
+        lib = _lib("gemm_tcgen05")
+        _check(lib, lib.pae_linear_swiglu_tcgen05(_ptr(out), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
+                                                  _ptr(_error_flag(x.device)), _stream()))
+        return out
+    return silu_mul(linear(x, weight), SWIGLU_BLOCK)
 
 
 def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> torch.Tensor:

@@ -26,13 +26,22 @@ class SwiGLU(Part):
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.intermediate_size = int(spec.params["intermediate_size"])
-        # Rows [0, I) are the gate, rows [I, 2I) the up projection.
-        self.gate_up_weight = torch.cat(
-            [tensors.pop(spec.tensor_name("gate_proj.weight")), tensors.pop(spec.tensor_name("up_proj.weight"))], dim=0
-        ).contiguous()
+        gate = tensors.pop(spec.tensor_name("gate_proj.weight"))
+        up = tensors.pop(spec.tensor_name("up_proj.weight"))
+        # Gate and up are one product. Where the kernels offer it, their rows alternate in
+        # blocks (16 gate rows, their 16 up rows, ...) so that SiLU x up runs inside the
+        # product; else rows [0, I) are the gate and rows [I, 2I) the up projection.
+        interleave = getattr(self.ops, "interleave_gate_up", None)
+        self.gate_up_weight = interleave(gate, up) if interleave is not None else None
+        self.interleaved = self.gate_up_weight is not None
+        if not self.interleaved:
+            self.gate_up_weight = torch.cat([gate, up], dim=0).contiguous()
         self.down_weight = tensors.pop(spec.tensor_name("down_proj.weight"))
 
     def forward(self, ctx, x, residual):
         ops = self.ops
-        gate_up = ops.linear(x, self.gate_up_weight, None)
-        return ops.linear(ops.silu_mul(gate_up), self.down_weight, None, residual)
+        if self.interleaved:
+            hidden = ops.linear_swiglu(x, self.gate_up_weight)
+        else:
+            hidden = ops.silu_mul(ops.linear(x, self.gate_up_weight, None))
+        return ops.linear(hidden, self.down_weight, None, residual)

@@ -122,3 +122,28 @@ def test_sum_fused_into_rotation_and_page_write(ops, heads, kv_heads, d, page):
     unfused = ops.rotary_qk_cache_write(plain.clone(), table, slots, caches[2], caches[3], heads, kv_heads, d, page)
     assert torch.equal(fused, unfused)
     assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+
+
+@pytest.mark.parametrize("m", [1, 8, 64, 65, 300, 2048])
+@pytest.mark.parametrize("inter,k", [(8960, 1536), (176, 64), (256, 96), (2000, 264)])
+def test_swiglu_inside_the_product(ops, m, inter, k):
+    """silu(gate) * up in the product's epilogue (many tokens), in the split sum (few tokens) and as
+    a kernel of its own give the same bits, and agree with the plain reference."""
+    x = _rand((m, k), 60)
+    gate = _rand((inter, k), 61, 0.05)
+    up = _rand((inter, k), 62, 0.05)
+    w = ops.interleave_gate_up(gate, up)
+    assert w is not None and tuple(w.shape) == (2 * inter, k)
+    assert torch.equal(w[:16], gate[:16]) and torch.equal(w[16:32], up[:16]) and torch.equal(w[32:48], gate[16:32])
+    got = ops.linear_swiglu(x, w)
+    ops.check_device_errors()
+    ops.use_tensor_cores = False
+    try:
+        apart = ops.silu_mul(ops.linear(x, w), 16)
+    finally:
+        ops.use_tensor_cores = True
+    want = ref.silu_mul(ref.linear(x.cpu(), torch.cat([gate, up]).cpu()).to(torch.bfloat16))
+    limit = 2.0 ** -6 * max(1e-3, float(want.float().abs().max()))
+    assert (got.float().cpu() - want.float()).abs().max().item() <= limit
+    assert (got.float() - apart.float()).abs().max().item() <= limit
+    assert ops.interleave_gate_up(gate[:24], up[:24]) is None, "an intermediate size that is no multiple of 16 stays apart"
