@@ -339,7 +339,8 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
 
 def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int) -> tuple[int, int]:
     """(keys per slice, slices) for the decode kernel: enough (request, kv head, slice) warps to
-    fill 148 SMs about twelve warps deep, slices of at least 32 keys in steps of 16."""
+    fill 148 SMs about twelve warps deep (fewer, longer slices were measured slower at every
+    batch size), slices of at least 32 keys in steps of 16."""
     wanted = max(1, min(64, -(-2048 // max(1, seqs * kv_heads))))
     slice_keys = max(32, -(-(-(-max_kv_len // wanted)) // 16) * 16)
     max_slices = -(-(max_kv_len + 15) // slice_keys)

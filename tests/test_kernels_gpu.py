@@ -233,8 +233,10 @@ def test_prefill_attention_portions_at_offsets(ops, heads, kv_heads, d, page, wi
     want = ref.paged_attention(*tensors, **args)
     got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
     _close(got, want, torch.bfloat16, scale=2.0)
+    # Knowing how many requests bring one token only changes how their keys are sliced: the
+    # same sums in another order.
     got2 = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=2)
-    assert torch.equal(got, got2)
+    assert (got.float() - got2.float()).abs().max().item() <= 2.0 ** -7 * float(got.float().abs().max())
 
 
 def test_tensor_core_attention_agrees_with_the_cuda_core_kernel(ops):

@@ -1,0 +1,82 @@
+"""The layer sizes of the Qwen2.5-1.5B shape (hidden 1536, 12 heads over 2 kv heads of 128,
+intermediate 8960, vocabulary 151936, tied head, theta 1e6), with two layers so that it stays
+quick: the kernels at the sizes they are tuned for (tcgen05 products and attention, split
+sums, SwiGLU in the epilogue), cut into portions and decoded, against the plain implementation
+run on the GPU in float32."""
+
+import pytest
+import torch
+
+import helpers
+from plain import qwen2_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+SHAPE = dict(
+    architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=1536, num_attention_heads=12,
+    num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936, rope_theta=1e6,
+    rms_norm_eps=1e-6, max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False,
+)
+
+
+@pytest.fixture(scope="module")
+def folder(tmp_path_factory):
+    return helpers.write_model(tmp_path_factory.mktemp("real_shape"), SHAPE, 3, torch.bfloat16, sharpen=2.0)
+
+
+@pytest.fixture(scope="module")
+def oracle(folder):
+    cfg = plain.read_config(folder)
+    weights = {k: v.float().cuda() for k, v in plain.read_weights(folder).items()}
+    requests = {"long": helpers.random_tokens(SHAPE["vocab_size"], 700, 1), "short": helpers.random_tokens(SHAPE["vocab_size"], 150, 2)}
+    logits = {}
+    for key, ids in requests.items():
+        ids_gpu = torch.tensor(ids, device="cuda")
+        hidden = plain.forward_hidden(ids_gpu, weights, cfg)
+        rows = list(range(0, len(ids), 37)) + [len(ids) - 1]
+        logits[key] = (rows, plain.linear(hidden[rows], plain.lm_head_weight(weights)).float().cpu())
+    del weights
+    torch.cuda.empty_cache()
+    return requests, logits
+
+
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
+def test_portions_and_decoding_at_the_real_layer_sizes(folder, oracle, dtype_name):
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.engine.replay import Replayer
+    from paged_attention_engine_b200.kernels import ops
+
+    requests, logits = oracle
+    dtype = torch.bfloat16 if dtype_name == "bfloat16" else torch.float32
+    engine = Engine.from_pretrained(folder, dtype_name)
+    replayer = Replayer(engine, max_tokens=1024, block_size=16)
+    # `long`: a portion of 400 (tcgen05 attention and persistent products in bfloat16), one of 236
+    # beside the whole of `short`, then single tokens; logits wanted at every 37th place.
+    long_ids, short_ids = requests["long"], requests["short"]
+    wanted = {key: set(rows) for key, (rows, _) in logits.items()}
+
+    def entry(key, ids, start, count):
+        want = [i for i in range(count) if start + i in wanted[key]]
+        return {"id": key, "tokens": ids[start : start + count], "want": want}
+
+    steps = [
+        {"step": 0, "entries": [entry("long", long_ids, 0, 400)], "end": []},
+        {"step": 1, "entries": [entry("long", long_ids, 400, 236), entry("short", short_ids, 0, 150)], "end": ["short"]},
+    ]
+    for i in range(636, 700):
+        steps.append({"step": len(steps), "entries": [entry("long", long_ids, i, 1)], "end": ["long"] if i == 699 else []})
+    got = {key: [] for key in requests}
+    for record in steps:
+        out = replayer.run(record)
+        ops.check_device_errors()
+        at = 0
+        for e in record["entries"]:
+            n = len(e["want"])
+            if n:
+                got[e["id"]].append(out[at : at + n].float().cpu())
+                at += n
+    for key, (rows, want) in logits.items():
+        have = torch.cat(got[key])
+        assert have.shape == want.shape
+        gap = (have - want).abs().max().item()
+        assert gap <= helpers.tolerance(dtype, want), f"{dtype_name}/{key}: max |dlogit| {gap:.3e} vs {helpers.tolerance(dtype, want):.3e}"
