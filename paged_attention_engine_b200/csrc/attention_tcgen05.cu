@@ -196,6 +196,11 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_v, const Params p) {
   using L = Layout<D>;
   dependent_launch_trigger();
+  if (threadIdx.x == 0) {         // the descriptors do not depend on the kernel before: fetch them early
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
   extern __shared__ uint8_t raw_smem[];
   const uint32_t raw = smem_u32(raw_smem);
   const uint32_t base = (raw + 1023u) & ~1023u;

@@ -279,6 +279,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
 
   dependent_launch_trigger();     // the kernel after this one may begin its own set-up
+  if (threadIdx.x == 0) {         // the descriptors do not depend on the kernel before: fetch them early
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_a = blockIdx.x, tile_b = blockIdx.y;
   const int kb_begin = blockIdx.z * p.kb_per_split;
@@ -306,17 +310,37 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  // Barriers and tensor memory are set up; from here on global memory is touched, which has
-  // to wait for the kernel before this one.
+  // Barriers and tensor memory are set up. The WEIGHT operand (A when the rows of the MMA are
+  // weight rows, else B) is never written during a step, so its first stages are fetched
+  // now, while the kernel before this one may still be running; everything else of global
+  // memory has to wait for that kernel.
+  const int early = min(kb_count, T::STAGES);
+  if (warp == 0 && lane == 0) {
+    for (int i = 0; i < early; ++i) {
+      const uint32_t a_dst = base + i * T::STAGE_BYTES;
+      mbar_expect_tx(full_bar(i), T::STAGE_BYTES);
+      if (MODE == SWAPPED)
+        tma_load_2d(a_dst, &map_a, full_bar(i), (kb_begin + i) * BK, tile_a * BM);
+      else
+        tma_load_2d(a_dst + T::A_BYTES, &map_b, full_bar(i), (kb_begin + i) * BK, tile_b * BN);
+    }
+  }
   dependent_launch_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < kb_count; ++i) {
+      int issued = early;
+      for (int i = 0; i < early; ++i) {          // the other operand of the stages begun above
+        const uint32_t a_dst = base + i * T::STAGE_BYTES;
+        if (MODE == SWAPPED)
+          tma_load_2d(a_dst + T::A_BYTES, &map_b, full_bar(i), (kb_begin + i) * BK, tile_b * BN);
+        else
+          tma_load_2d(a_dst, &map_a, full_bar(i), (kb_begin + i) * BK, tile_a * BM);
+      }
+      for (int i = early; i < kb_count; ++i) {
         const int s = i % T::STAGES;
-        if (i >= T::STAGES && !mbar_wait(empty_bar(s), ((i / T::STAGES) - 1) & 1, abort_flag, p.error, 1)) break;
+        if (!mbar_wait(empty_bar(s), ((i / T::STAGES) - 1) & 1, abort_flag, p.error, 1)) break;
         const uint32_t a_dst = base + s * T::STAGE_BYTES;
         mbar_expect_tx(full_bar(s), T::STAGE_BYTES);
         tma_load_2d(a_dst, &map_a, full_bar(s), (kb_begin + i) * BK, tile_a * BM);
@@ -425,6 +449,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
   constexpr int P_STAGE_BYTES = PTile<PBN>::STAGE_BYTES;
   constexpr int ACC = PTile<PBN>::ACC_COLUMNS;
   dependent_launch_trigger();
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+  }
   extern __shared__ uint8_t raw_smem[];
   const uint32_t raw = smem_u32(raw_smem);
   const uint32_t base = (raw + 1023u) & ~1023u;
