@@ -236,27 +236,28 @@ struct DecodeParams {
 
 template <int D>
 __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const DecodeParams p) {
-  dependent_launch_prologue();
+  // The step's integers (starts, lengths, block tables) were copied in before the step began
+  // and the keys and values of EARLIER tokens are not written by any kernel of this step, so
+  // a slice's first tile is fetched before the wait for the kernel that precedes this one
+  // (which writes this step's queries, keys and values). Every block waits before it leaves.
+  dependent_launch_trigger();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slice = blockIdx.x * DECODE_WARPS + warp;
   const int g = blockIdx.y, b = blockIdx.z;
   const int token = p.q_start[b];
-  if (p.q_start[b + 1] - token != 1 || slice >= p.max_slices) return;      // not a single-token request
   const int kv_len = p.kv_len[b];
   const int first_key = p.window > 0 ? max(0, kv_len - p.window) : 0;     // the query stands at kv_len - 1
   const int base = (first_key / TILE_KEYS) * TILE_KEYS;
   const int begin = base + slice * p.slice_keys;
   const int end = min(kv_len, begin + p.slice_keys);
-  if (begin >= kv_len) return;
+  if (p.q_start[b + 1] - token != 1 || slice >= p.max_slices || begin >= kv_len) {   // nothing for this warp
+    dependent_launch_wait();
+    return;
+  }
 
   const int groups = p.heads / p.kv_heads;
   const int row_elems = (p.heads + 2 * p.kv_heads) * D;
-  uint32_t q[D / 16][4];
-  load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
-    return r < groups ? p.qkv + (size_t)token * row_elems + (size_t)(g * groups + r) * D : nullptr;
-  });
-
   constexpr int TILE_BYTES = TILE_KEYS * D * 2;
   uint8_t* mine = smem + warp * 4 * TILE_BYTES;             // two stages of (K tile, V tile)
   const uint32_t mine_u32 = smem_u32(mine);
@@ -276,14 +277,22 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const 
     }
   };
 
+  const bool early = begin + TILE_KEYS <= kv_len - 1;       // the first tile holds earlier tokens only
+  if (early) fetch(0, begin);
+  dependent_launch_wait();
+  uint32_t q[D / 16][4];
+  load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
+    return r < groups ? p.qkv + (size_t)token * row_elems + (size_t)(g * groups + r) * D : nullptr;
+  });
+  if (!early) fetch(0, begin);
+  cp_async_commit();
+
   float o[D / 8][4];
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float row_max[2] = {-FLT_MAX, -FLT_MAX}, row_sum[2] = {0.f, 0.f};
 
   const int tiles = (end - begin + TILE_KEYS - 1) / TILE_KEYS;
-  fetch(0, begin);
-  cp_async_commit();
   for (int t = 0; t < tiles; ++t) {
     if (t + 1 < tiles) fetch((t + 1) & 1, begin + (t + 1) * TILE_KEYS);
     cp_async_commit();
