@@ -98,6 +98,27 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
   cudaLaunchKernelEx(&config, kernel, KArgs(std::forward<Args>(args))...);   // errors surface in check_launch
 }
 
+// The same for a kernel whose blocks form clusters of `cluster_x` along x (distributed shared memory).
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = cluster_x;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&config, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 }  // namespace pae
 
 #define PAE_EXPORT extern "C" __attribute__((visibility("default")))

@@ -337,14 +337,24 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
     return qkv
 
 
-def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int) -> tuple[int, int]:
+def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64) -> tuple[int, int]:
     """(keys per slice, slices) for the decode kernel: enough (request, kv head, slice) warps to
     fill 148 SMs about twelve warps deep (fewer, longer slices were measured slower at every
-    batch size), slices of at least 32 keys in steps of 16."""
-    wanted = max(1, min(64, -(-2048 // max(1, seqs * kv_heads))))
+    batch size), slices of at least 32 keys in steps of 16, at most `most` slices."""
+    wanted = max(1, min(most, -(-2048 // max(1, seqs * kv_heads))))
     slice_keys = max(32, -(-(-(-max_kv_len // wanted)) // 16) * 16)
-    max_slices = -(-(max_kv_len + 15) // slice_keys)
-    return slice_keys, max_slices
+    while -(-(max_kv_len + 15) // slice_keys) > most:
+        slice_keys += 16
+    return slice_keys, -(-(max_kv_len + 15) // slice_keys)
+
+
+# Whether the slices of decode attention are merged on chip by thread-block clusters
+# (distributed shared memory, one kernel, no scratch) when there are enough (request, kv head)
+# pairs to fill the machine with 32 slices each. Measured slower than slices through scratch
+# plus a merge kernel at the benchmark's sizes (14.6 against 12.2 us per layer at batch 8,
+# context 4096), so it is off; tests run both.
+use_cluster_decode = False
+CLUSTER_DECODE_MIN_PAIRS = 8
 
 
 use_tcgen05_attention = True
@@ -354,14 +364,21 @@ TCGEN05_ATTENTION_MIN_TOKENS = 64
 def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
                       num_kv_heads, head_dim, page_size, max_kv_len, scale, window) -> None:
     """The requests that bring one token: sliced over their keys, then merged."""
-    slice_keys, max_slices = decode_slicing(seqs if singles < 0 else singles, num_kv_heads, max_kv_len)
-    floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
-    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+    count = seqs if singles < 0 else singles
+    scratch = None
+    if use_cluster_decode and count * num_kv_heads >= CLUSTER_DECODE_MIN_PAIRS:
+        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, most=32)
+        launches = 1
+    else:
+        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len)
+        floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
+        scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+        launches = 2
     _check(lib, lib.pae_paged_attention_decode(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_float(scale), c_int(window), c_int(slice_keys), c_int(max_slices),
-        _ptr(scratch), _stream()), 2)
+        _ptr(scratch), _stream()), launches)
 
 
 def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,

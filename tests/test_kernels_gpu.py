@@ -216,6 +216,14 @@ def test_decode_attention_over_long_contexts(ops, heads, kv_heads, d, page, wind
     want = ref.paged_attention(*tensors, **args)
     got = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=len(kv))
     _close(got, want, torch.bfloat16, scale=2.0)
+    # The slices merged on chip by a cluster, and merged through scratch by a second kernel.
+    ops.use_cluster_decode = True
+    try:
+        other = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=len(kv))
+    finally:
+        ops.use_cluster_decode = False
+    _close(other, want, torch.bfloat16, scale=2.0)
+    assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -7 * float(want.abs().max())
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [
