@@ -239,12 +239,14 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   dependent_launch_wait();
 
   // ---- what this block works on (the same in every role) -------------------------------
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   const int q_tiles = (q_count + BQ - 1) / BQ;
-  // Late tiles see the most keys: they go first, the short early ones fill in behind them.
-  const int tile = q_tiles - 1 - (int)blockIdx.x;
+  // Late tiles see the most keys: they go first in every head (the head is the fastest grid
+  // index, so the first wave holds the longest blocks of all heads), the short early ones
+  // fill in behind them.
+  const int tile = q_tiles - 1 - (int)blockIdx.y;
   const bool active = tile >= 0 && !(p.skip_single && q_count == 1);
   const int rows = active ? min(BQ, q_count - tile * BQ) : 0;
   const int pos0 = p.q_pos0[b] + tile * BQ;
@@ -550,7 +552,7 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
     if (err != cudaSuccess) return fail(100, "paged_attention_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
-  dim3 grid((max_q_len + BQ - 1) / BQ, p.heads, seqs);
+  dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
   launch_kernel(prefill_tcgen05_kernel<D>, grid, THREADS, L::SMEM_BYTES, stream, map_q, map_k, map_v, p);
   return check_launch("paged_attention_tcgen05");
 }
