@@ -10,6 +10,31 @@ PAE_EXPORT int pae_attention_mma_supports(int heads, int kv_heads, int d, int pa
          heads % kv_heads == 0 && heads / kv_heads <= 16;
 }
 
+// How many blocks of the decode kernel (four slices each) the device holds at one time: the
+// slicing aims at one such wave, since a second, partly filled one costs as much as a full one.
+PAE_EXPORT int pae_decode_blocks_per_wave(int d) {
+  static int cached[3] = {0, 0, 0};
+  const int which = d == 32 ? 0 : (d == 64 ? 1 : 2);
+  if (cached[which] == 0) {
+    int device = 0, sms = 148, per_sm = 0;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const size_t bytes = (size_t)DECODE_WARPS * 4 * TILE_KEYS * (d == 32 ? 32 : (d == 64 ? 64 : 128)) * 2;
+    cudaError_t err;
+    if (d == 32) {
+      allow_smem(decode_slices_kernel<32>, bytes, "paged_attention_decode");
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<32>, DECODE_WARPS * 32, bytes);
+    } else if (d == 64) {
+      allow_smem(decode_slices_kernel<64>, bytes, "paged_attention_decode");
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<64>, DECODE_WARPS * 32, bytes);
+    } else {
+      allow_smem(decode_slices_kernel<128>, bytes, "paged_attention_decode");
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<128>, DECODE_WARPS * 32, bytes);
+    }
+    cached[which] = (err == cudaSuccess && per_sm > 0 ? per_sm : 1) * sms;
+  }
+  return cached[which];
+}
+
 // Floats of scratch that `pae_paged_attention_decode` needs for `seqs` requests and `max_slices` slices.
 PAE_EXPORT long long pae_decode_scratch_floats(int seqs, int heads, int d, int max_slices) {
   return decode_scratch_floats(seqs, heads, d, max_slices);

@@ -337,13 +337,16 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
     return qkv
 
 
-def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64) -> tuple[int, int]:
-    """(keys per slice, slices) for the decode kernel: enough (request, kv head, slice) warps to
-    fill 148 SMs about twelve warps deep (fewer, longer slices were measured slower at every
-    batch size), slices of at least 32 keys in steps of 16, at most `most` slices."""
-    wanted = max(1, min(most, -(-2048 // max(1, seqs * kv_heads))))
+def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64, wave_blocks: int = 444) -> tuple[int, int]:
+    """(keys per slice, slices) for the decode kernel. A block is four slices of one (request,
+    kv head) pair, and `wave_blocks` blocks run at one time: as many slices as keep all blocks
+    in that one wave (a second, partly filled wave costs as much as a full one), at most
+    `most`, each of at least 32 keys in steps of 16."""
+    pairs = max(1, seqs * kv_heads)
+    blocks_per_pair = max(1, wave_blocks // pairs)
+    wanted = max(1, min(most, 4 * blocks_per_pair))
     slice_keys = max(32, -(-(-(-max_kv_len // wanted)) // 16) * 16)
-    while -(-(max_kv_len + 15) // slice_keys) > most:
+    while -(-(max_kv_len + 15) // slice_keys) > wanted:
         slice_keys += 16
     return slice_keys, -(-(max_kv_len + 15) // slice_keys)
 
@@ -370,7 +373,8 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
         slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, most=32)
         launches = 1
     else:
-        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len)
+        wave = lib.pae_decode_blocks_per_wave(c_int(head_dim))
+        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave)
         floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
         scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
         launches = 2
