@@ -64,4 +64,5 @@ class DecoderModel:
         if ctx.logit_rows.numel() == 0:
             return None
         rows = self.ops.gather_rows(hidden, ctx.logit_rows)
-        return self.head.forward(ctx, self.final_norm.forward(ctx, rows))
+        # The head's product may still be waiting for its sum (a step of few wanted rows): logits leave as a tensor.
+        return self.ops.materialized(self.head.forward(ctx, self.final_norm.forward(ctx, rows)))

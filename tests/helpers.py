@@ -57,7 +57,14 @@ TINY_C = dict(
     rms_norm_eps=3e-6, max_position_embeddings=512, tie_word_embeddings=False, use_sliding_window=True,
     sliding_window=24, max_window_layers=2,
 )
-TINY = {"tiny_a": (TINY_A, 4, 0), "tiny_b": (TINY_B, 16, 1), "tiny_c": (TINY_C, 8, 2)}  # config, page size, seed
+# D is wide enough for the tensor-core kernels' other forms: head_dim 64 (tcgen05 attention for long
+# portions), K of 256 and 512 (products whose K is split, the LM head among them).
+TINY_D = dict(
+    architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=256, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=1000, rope_theta=1e6,
+    rms_norm_eps=1e-6, max_position_embeddings=512, tie_word_embeddings=True, use_sliding_window=False,
+)
+TINY = {"tiny_a": (TINY_A, 4, 0), "tiny_b": (TINY_B, 16, 1), "tiny_c": (TINY_C, 8, 2), "tiny_d": (TINY_D, 16, 3)}  # config, page size, seed
 
 
 def write_model(folder: Path, raw: dict, seed: int, dtype: torch.dtype, sharpen: float = 1.0) -> Path:
