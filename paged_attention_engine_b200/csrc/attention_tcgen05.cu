@@ -506,6 +506,388 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
 }
 
 // ---------------------------------------------------------------------------------------
+// The paired form, for launches of at least two blocks per SM (long prompts, many requests or
+// heads). A block walks the keys 64 at a time with one softmax thread per query row, and
+// keeps O in tensor memory over all tiles instead of reading each tile's product back:
+// 113 KB of shared memory, 256 columns of tensor memory and 192 threads, so two blocks share
+// an SM and the softmax of one overlaps the products and the waits of the other.
+//
+// The reference of a row is its running maximum, but it only moves when the maximum has grown
+// by more than 2^8 since it was set: probabilities then stay below 256, which float32 sums and
+// the bfloat16 operand hold as well as values below 1, and the output in tensor memory (which
+// must be multiplied by 2^(old - new) whenever the reference moves) is touched on a row's first
+// tiles only. The sum is kept against the same reference, so the quotient is exact softmax.
+// ---------------------------------------------------------------------------------------
+namespace paired {
+
+constexpr int BKEYS = 64;           // keys per tile
+constexpr int THREADS = 192;        // TMA warp, MMA warp, four softmax warps (one thread per query row)
+constexpr int SOFTMAX_WARPS = 4;
+constexpr int KV_STAGES = 2;
+constexpr float REFERENCE_SLACK = 8.f;   // a row's reference follows its maximum in steps of more than 2^8
+
+// The same 32 columns written back (the whole warp calls it).
+__device__ __forceinline__ void tmem_store32(uint32_t address, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(address), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+template <int D>
+struct Layout {
+  static constexpr int HALVES = D / 64;                       // 64-column k-blocks of the head dimension
+  static constexpr int Q_HALF_BYTES = BQ * 128;               // 128 rows x 64 bfloat16
+  static constexpr int KV_HALF_BYTES = BKEYS * 128;           // 64 rows x 64 bfloat16
+  static constexpr int Q_BYTES = HALVES * Q_HALF_BYTES;
+  static constexpr int KV_BYTES = HALVES * KV_HALF_BYTES;     // one stage of K, or of V
+  static constexpr int P_BYTES = BQ * BKEYS * 2;              // 128 rows x 64 keys: one swizzle row each
+  static constexpr int Q_OFFSET = 0;
+  static constexpr int K_OFFSET = Q_BYTES;                    // two stages
+  static constexpr int V_OFFSET = K_OFFSET + KV_STAGES * KV_BYTES;
+  static constexpr int P_OFFSET = V_OFFSET + KV_STAGES * KV_BYTES;
+  static constexpr int BAR_OFFSET = P_OFFSET + P_BYTES;
+  static constexpr int USED_BYTES = BAR_OFFSET + 256;
+  // 768 bytes of slack for the 1024-byte alignment of the tiles: with it two blocks of head
+  // size 128 still fit on one SM. The kernel checks that the slack was enough.
+  static constexpr size_t SMEM_BYTES = (size_t)USED_BYTES + 768;
+  static constexpr int S_COLUMNS = BKEYS;                     // per score buffer
+  static constexpr int O_COLUMN = 2 * S_COLUMNS;              // O behind the two score buffers
+  static constexpr int TMEM_COLUMNS = 256;
+};
+
+enum Bar : int {
+  Q_FULL = 0, O_FULL = 1, S_FULL = 2, S_EMPTY = 4, P_READY = 6, P_EMPTY = 7,
+  K_FULL = 8, K_EMPTY = K_FULL + KV_STAGES, V_FULL = K_EMPTY + KV_STAGES, V_EMPTY = V_FULL + KV_STAGES, NUM_BARS = V_EMPTY + KV_STAGES
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                     const __grid_constant__ CUtensorMap map_k,
+                                                                     const __grid_constant__ CUtensorMap map_v, const Params p) {
+  using L = Layout<D>;
+  dependent_launch_trigger();
+  if (threadIdx.x == 0) {         // the descriptors do not depend on the kernel before: fetch them early
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+  }
+  extern __shared__ __align__(1024) uint8_t raw_smem[];
+  const uint32_t raw = smem_u32(raw_smem);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* generic_base = raw_smem + (base - raw);
+  const uint32_t bars = base + L::BAR_OFFSET;
+  volatile uint32_t* tmem_holder = (volatile uint32_t*)(generic_base + L::BAR_OFFSET + 8 * NUM_BARS);
+  volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+  auto bar = [&](int which, int i = 0) { return bars + 8u * (which + i); };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool fits = (base - raw) + (uint32_t)L::USED_BYTES <= (uint32_t)L::SMEM_BYTES;
+  if (!fits) {                     // the alignment took more than the slack: nothing is touched
+    if (threadIdx.x == 0) atomicCAS(p.error, 0, 20);
+    return;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(Q_FULL), 1);
+    for (int i = 0; i < KV_STAGES; ++i) {
+      mbar_init(bar(K_FULL, i), 1);
+      mbar_init(bar(K_EMPTY, i), 1);
+      mbar_init(bar(V_FULL, i), 1);
+      mbar_init(bar(V_EMPTY, i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(S_FULL, i), 1);
+      mbar_init(bar(S_EMPTY, i), SOFTMAX_WARPS);     // one arrival per warp
+    }
+    mbar_init(bar(P_READY), SOFTMAX_WARPS);
+    mbar_init(bar(P_EMPTY), 1);                      // by tcgen05.commit: the second product has read P
+    mbar_init(bar(O_FULL), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32((const void*)tmem_holder), L::TMEM_COLUMNS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  dependent_launch_wait();
+
+  // ---- what this block works on (the same in every role) -------------------------------
+  const int h = blockIdx.x, b = blockIdx.z;
+  const int first_token = p.q_start[b];
+  const int q_count = p.q_start[b + 1] - first_token;
+  const int q_tiles = (q_count + BQ - 1) / BQ;
+  // Late tiles see the most keys: they go first in every head (the head is the fastest grid
+  // index, so the first wave holds the longest blocks of all heads), the short early ones
+  // fill in behind them.
+  const int tile = q_tiles - 1 - (int)blockIdx.y;
+  const bool active = tile >= 0 && !(p.skip_single && q_count == 1);
+  const int rows = active ? min(BQ, q_count - tile * BQ) : 0;
+  const int pos0 = p.q_pos0[b] + tile * BQ;
+  const int kv_end = active ? min(p.kv_len[b], pos0 + rows) : 0;
+  const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int kv_begin = (first_key / BKEYS) * BKEYS;
+  const int n_tiles = active ? (kv_end - kv_begin + BKEYS - 1) / BKEYS : 0;
+  const int g = h / (p.heads / p.kv_heads);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    // Lane i brings box i of a tile (its block-table entry and its copies), so the table
+    // look-ups of a tile are one round trip, not one per page. A box is a page, or the 64
+    // rows of a larger page that the tile covers. Lane 0 posts the byte counts before any
+    // lane issues a copy.
+    if (active) {
+      if (lane == 0) {
+        mbar_expect_tx(bar(Q_FULL), L::Q_BYTES);
+#pragma unroll
+        for (int half = 0; half < L::HALVES; ++half)
+          tma_load_2d(base + L::Q_OFFSET + half * L::Q_HALF_BYTES, &map_q, bar(Q_FULL), h * D + half * 64,
+                      first_token + tile * BQ);
+      }
+      const int* table = p.block_table + (size_t)b * p.table_width;
+      const int box_rows = min(p.page_size, BKEYS);
+      const int boxes = BKEYS / box_rows;
+      const int last_page = (kv_end - 1) / p.page_size;          // the last page that holds a visible key
+      const bool mine = lane < boxes;
+      // A page past the last visible key may not exist: its rows are masked, so any page of
+      // the request will do; the last visible one is taken.
+      auto box_row = [&](int t) {
+        const int key = kv_begin + t * BKEYS + lane * box_rows;
+        const int page = table[min(key / p.page_size, last_page)];
+        return (page * p.kv_heads + g) * p.page_size + key % p.page_size;
+      };
+      int row = mine ? box_row(0) : 0;
+      int issued = 0;
+      bool ok = true;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int stage = t % KV_STAGES;
+        const uint32_t round = (uint32_t)(t / KV_STAGES);
+        int next_row = 0;
+        if (mine && t + 1 < n_tiles) next_row = box_row(t + 1);
+        if (t >= KV_STAGES) {
+          if (lane == 0) ok = mbar_wait(bar(K_EMPTY, stage), (round - 1) & 1, abort_flag, p.error, 1);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
+        if (lane == 0) mbar_expect_tx(bar(K_FULL, stage), L::KV_BYTES);
+        __syncwarp();
+        const uint32_t dst = stage * L::KV_BYTES + lane * box_rows * 128;
+        if (mine) {
+#pragma unroll
+          for (int half = 0; half < L::HALVES; ++half)
+            tma_load_2d(base + L::K_OFFSET + dst + half * L::KV_HALF_BYTES, &map_k, bar(K_FULL, stage), half * 64, row);
+        }
+        if (t >= KV_STAGES) {
+          if (lane == 0) ok = mbar_wait(bar(V_EMPTY, stage), (round - 1) & 1, abort_flag, p.error, 10);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
+        if (lane == 0) mbar_expect_tx(bar(V_FULL, stage), L::KV_BYTES);
+        __syncwarp();
+        if (mine) {
+#pragma unroll
+          for (int half = 0; half < L::HALVES; ++half)
+            tma_load_2d(base + L::V_OFFSET + dst + half * L::KV_HALF_BYTES, &map_v, bar(V_FULL, stage), half * 64, row);
+        }
+        row = next_row;
+        issued = t + 1;
+      }
+      if (lane == 0 && *abort_flag) {      // copies that were issued still write into this block's shared memory
+        for (int t = max(0, issued - KV_STAGES); t < issued; ++t) {
+          for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar(K_FULL, t % KV_STAGES), (t / KV_STAGES) & 1); ++w) __nanosleep(64);
+          for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar(V_FULL, t % KV_STAGES), (t / KV_STAGES) & 1); ++w) __nanosleep(64);
+        }
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar(Q_FULL), 0); ++w) __nanosleep(64);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && active) {
+      constexpr uint32_t idesc_s = instruction_descriptor(BQ, BKEYS, false);
+      constexpr uint32_t idesc_o = instruction_descriptor(BQ, D, true);
+      bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.error, 2);
+      auto issue_scores = [&](int t) {
+        const int st = t & 1, stage = t % KV_STAGES;
+        ok = ok && mbar_wait(bar(K_FULL, stage), (t / KV_STAGES) & 1, abort_flag, p.error, 3);
+        if (t >= 2) ok = ok && mbar_wait(bar(S_EMPTY, st), ((t >> 1) - 1) & 1, abort_flag, p.error, 4);
+        if (!ok) return;
+        tcgen05_fence_after();
+        const uint32_t q_addr = base + L::Q_OFFSET, k_addr = base + L::K_OFFSET + stage * L::KV_BYTES;
+#pragma unroll
+        for (int half = 0; half < L::HALVES; ++half)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_base + st * L::S_COLUMNS, k_major_descriptor(q_addr + half * L::Q_HALF_BYTES + k * 32),
+                      k_major_descriptor(k_addr + half * L::KV_HALF_BYTES + k * 32), idesc_s, (half > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(bar(S_FULL, st));
+        tcgen05_commit(bar(K_EMPTY, stage));    // the K stage is free once these MMAs have read it
+      };
+      if (n_tiles > 0) issue_scores(0);
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (t + 1 < n_tiles) issue_scores(t + 1);
+        const int st = t & 1, stage = t % KV_STAGES;
+        ok = ok && mbar_wait(bar(V_FULL, stage), (t / KV_STAGES) & 1, abort_flag, p.error, 5);
+        ok = ok && mbar_wait(bar(P_READY), t & 1, abort_flag, p.error, 6);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t p_addr = base + L::P_OFFSET, v_addr = base + L::V_OFFSET + stage * L::KV_BYTES;
+#pragma unroll
+        for (int k = 0; k < BKEYS / 16; ++k)     // 16 keys a step: two groups of 8 rows of V
+          umma_bf16(tmem_base + L::O_COLUMN, k_major_descriptor(p_addr + k * 32),
+                    mn_major_descriptor(v_addr + k * 2048, L::KV_HALF_BYTES), idesc_o, (t > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(bar(P_EMPTY));            // P may be written again, and O is at rest until the next P is ready
+        tcgen05_commit(bar(V_EMPTY, stage));
+      }
+      if (ok) tcgen05_commit(bar(O_FULL));       // the output is complete
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax, one thread per row
+    const int quadrant = warp & 3;
+    const int r = quadrant * 32 + lane;                       // row of the tile, lane of tensor memory
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quadrant * 32) << 16);
+    const int my_pos = pos0 + r;
+    float reference = -FLT_MAX, row_sum = 0.f;                // the reference in units of log2, scaled
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t & 1;
+      uint8_t* p_row = generic_base + L::P_OFFSET + r * 128;
+      const int key0 = kv_begin + t * BKEYS;
+      ok = ok && mbar_wait(bar(S_FULL, st), (t >> 1) & 1, abort_flag, p.error, 8);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tcgen05_fence_after();
+      // The whole tile is visible to every row of the block: no mask. Otherwise a row sees the
+      // keys lo..hi of the request (nothing when the row is past the request's tokens).
+      const bool unmasked = key0 + BKEYS - 1 <= pos0 && key0 + BKEYS <= kv_end && key0 >= first_key &&
+                            (p.window <= 0 || pos0 + rows - 1 - key0 < p.window);
+      const int hi = r < rows ? min(my_pos, kv_end - 1) - key0 : -1;          // relative to the tile
+      const int lo = (p.window > 0 ? max(first_key, my_pos - p.window + 1) : first_key) - key0;
+      float s[BKEYS];
+      tmem_load32(lane_base + st * L::S_COLUMNS, s);
+      tmem_load32(lane_base + st * L::S_COLUMNS + 32, s + 32);
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(S_EMPTY, st));             // the scores are in registers
+      float m4[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX};
+      if (unmasked) {
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) m4[i & 3] = fmaxf(m4[i & 3], s[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) m4[i & 3] = fmaxf(m4[i & 3], (i >= lo && i <= hi) ? s[i] : -FLT_MAX);
+      }
+      float tile_max = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      if (tile_max != -FLT_MAX) tile_max *= p.scale_log2;        // the scale is positive: max(s) scales with it
+      // The second product of the tile before has completed: P may be written, O is at rest.
+      if (t >= 1) ok = mbar_wait(bar(P_EMPTY), (t - 1) & 1, abort_flag, p.error, 7);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const bool moves = tile_max > reference + REFERENCE_SLACK || (reference == -FLT_MAX && tile_max != -FLT_MAX);
+      if (__any_sync(0xffffffffu, moves)) {
+        // Some row of this warp moves its reference: its sum and its row of O are multiplied
+        // by 2^(old - new); the other rows by 1. Reading and writing tensor memory takes the whole warp.
+        const float shrink = !moves ? 1.f : (reference == -FLT_MAX ? 0.f : fast_exp2(reference - tile_max));
+        if (moves) {
+          reference = tile_max;
+          row_sum *= shrink;
+        }
+        if (t >= 1) {
+          tcgen05_fence_after();
+#pragma unroll
+          for (int c = 0; c < D; c += 32) {
+            float o[32];
+            tmem_load32(lane_base + L::O_COLUMN + c, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= shrink;
+            tmem_store32(lane_base + L::O_COLUMN + c, o);
+          }
+        }
+      }
+      // exp2(s * scale - reference) as one fused multiply-add and one ex2; a row that has seen
+      // no key yet has no reference and every probability 0.
+      const float offset = reference == -FLT_MAX ? 0.f : -reference;
+      const float factor = reference == -FLT_MAX ? 0.f : p.scale_log2;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (unmasked) {
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) {
+          s[i] = fast_exp2(fmaf(s[i], factor, offset));
+          sum4[i & 3] += s[i];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BKEYS; ++i) {
+          const float e = fast_exp2(fmaf(s[i], factor, offset));
+          s[i] = (i >= lo && i <= hi && factor != 0.f) ? e : 0.f;
+          sum4[i & 3] += s[i];
+        }
+      }
+      row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // 64 keys = eight 16-byte chunks of this row, swizzled by the row.
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 packed;
+        __nv_bfloat162* h2 = (__nv_bfloat162*)&packed;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(s[j * 8 + 2 * e], s[j * 8 + 2 * e + 1]);
+        *(uint4*)(p_row + ((j ^ (r & 7)) << 4)) = packed;
+      }
+      tcgen05_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core's eyes
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_READY));
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (active && ok && n_tiles > 0) {
+      ok = mbar_wait(bar(O_FULL), 0, abort_flag, p.error, 9);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tcgen05_fence_after();
+        const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+        __nv_bfloat16* out = p.out + ((size_t)(first_token + tile * BQ + r) * p.heads + h) * D;
+#pragma unroll
+        for (int c = 0; c < D; c += 32) {
+          float o[32];
+          tmem_load32(lane_base + L::O_COLUMN + c, o);        // every lane takes part
+          if (r < rows) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 packed;
+              __nv_bfloat162* h2 = (__nv_bfloat162*)&packed;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[j * 8 + 2 * e] * inv, o[j * 8 + 2 * e + 1] * inv);
+              *(uint4*)(out + c + j * 8) = packed;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, L::TMEM_COLUMNS);
+  }
+}
+
+}  // namespace paired
+
+// ---------------------------------------------------------------------------------------
 using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -537,23 +919,43 @@ int tensor_map(CUtensorMap* out, const void* ptr, long long rows, int cols, int 
   return 0;
 }
 
+int sm_count() {
+  static int count = [] {
+    int device = 0, n = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+    return n;
+  }();
+  return count;
+}
+
+// form 0: the paired kernel when the launch has at least two blocks per SM, else the wide one;
+// 1: wide; 2: paired.
 template <int D>
 int launch(const Params& p, const void* qkv, const void* keys, const void* values, int tokens, long long pages, int seqs,
-           int max_q_len, cudaStream_t stream) {
-  using L = Layout<D>;
+           int max_q_len, int form, cudaStream_t stream) {
+  dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
+  const bool use_paired = form == 2 || (form == 0 && (long long)grid.x * grid.y * grid.z >= 2LL * sm_count());
   CUtensorMap map_q, map_k, map_v;
   if (int err = tensor_map(&map_q, qkv, tokens, (p.heads + 2 * p.kv_heads) * D, BQ)) return err;
   const long long cache_rows = pages * p.kv_heads * p.page_size;
-  if (int err = tensor_map(&map_k, keys, cache_rows, D, p.page_size)) return err;
-  if (int err = tensor_map(&map_v, values, cache_rows, D, p.page_size)) return err;
+  const int tile_keys = use_paired ? paired::BKEYS : BKEYS;
+  const int box_rows = p.page_size < tile_keys ? p.page_size : tile_keys;
+  if (int err = tensor_map(&map_k, keys, cache_rows, D, box_rows)) return err;
+  if (int err = tensor_map(&map_v, values, cache_rows, D, box_rows)) return err;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES);
+    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<D>::SMEM_BYTES);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(paired::prefill_tcgen05_paired_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)paired::Layout<D>::SMEM_BYTES);
     if (err != cudaSuccess) return fail(100, "paged_attention_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
-  dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
-  launch_kernel(prefill_tcgen05_kernel<D>, grid, THREADS, L::SMEM_BYTES, stream, map_q, map_k, map_v, p);
+  if (use_paired)
+    launch_kernel(paired::prefill_tcgen05_paired_kernel<D>, grid, paired::THREADS, paired::Layout<D>::SMEM_BYTES, stream, map_q, map_k,
+                  map_v, p);
+  else
+    launch_kernel(prefill_tcgen05_kernel<D>, grid, THREADS, Layout<D>::SMEM_BYTES, stream, map_q, map_k, map_v, p);
   return check_launch("paged_attention_tcgen05");
 }
 
@@ -565,12 +967,13 @@ PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, in
 }
 
 // Attention of every request that brings more than one token (or every request, unless
-// skip_single). qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
+// skip_single). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests). qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
 PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, const void* keys, const void* values,
                                                    long long pages, const int* block_table, int table_width,
                                                    const int* q_start, const int* q_pos0, const int* kv_len, int tokens,
                                                    int seqs, int max_q_len, int heads, int kv_heads, int d, int page_size,
-                                                   float scale, int window, int skip_single, int* error, void* stream) {
+                                                   float scale, int window, int skip_single, int form, int* error,
+                                                   void* stream) {
   if (seqs == 0 || max_q_len == 0 || tokens == 0) return 0;
   if (!pae_attention_tcgen05_supports(heads, kv_heads, d, page_size))
     return fail(2, "paged_attention_tcgen05: head_dim %d with pages of %d is not taken (64 or 128; 16, 32, 64 or 128)", d, page_size);
@@ -592,8 +995,8 @@ PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, c
   p.scale_log2 = scale * LOG2E;
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
-  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, s);
-  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, s);
+  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, form, s);
+  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, form, s);
 }
 
 PAE_DEFINE_LAST_ERROR()

@@ -175,9 +175,11 @@ def test_sampling(ops, vocab):
             assert scores[got[r]].item() >= scores.max().item() - 1e-4
 
 
-def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True):
+def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True, late_spike=False):
     """Random queries, keys and values over shuffled pages. With `spike`, one far key of every
-    request (its key 3) is made to score high for every query, so that missing it shows."""
+    request (its key 3) is made to score high for every query, so that missing it shows. With
+    `late_spike`, a key 40 places before a request's end scores far higher still than anything
+    before it: a row's maximum then jumps by more than 2^8 in the middle of its walk over the keys."""
     kv_lens = [p + n for p, n in zip(pos0, q_lens)]
     width = max(-(-n // page) for n in kv_lens)
     total_pages = sum(-(-n // page) for n in kv_lens) + 5
@@ -197,6 +199,9 @@ def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True):
         for b, n in enumerate(kv_lens):
             j = min(3, n - 1)
             keys[table[b, j // page], :, j % page] += 3.0 * direction
+            if late_spike and n > 80:
+                j = n - 40
+                keys[table[b, j // page], :, j % page] += 40.0 * direction
     q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), dtype=torch.int32)
     tensors = [qkv.to(dtype), keys.to(dtype), values.to(dtype), table, q_start,
                torch.tensor(pos0, dtype=torch.int32), torch.tensor(kv_lens, dtype=torch.int32)]
@@ -265,18 +270,25 @@ def test_tensor_core_attention_agrees_with_the_cuda_core_kernel(ops):
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [
     (12, 2, 128, 16, 0), (4, 4, 64, 16, 0), (3, 1, 128, 32, 0), (6, 3, 128, 16, 100), (2, 1, 64, 64, 17), (5, 5, 128, 128, 0),
 ])
-def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window):
-    """The tcgen05 form: portions of 64 tokens and more at offsets that are ragged against its
-    128-row tiles, the pages and the 128-key tiles, beside shorter portions and single tokens."""
+@pytest.mark.parametrize("form,late_spike", [(1, False), (2, False), (1, True), (2, True)])
+def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window, form, late_spike):
+    """The tcgen05 kernels (form 1: 128-key tiles, one block per SM; form 2: 64-key tiles, the
+    output kept in tensor memory, two blocks per SM): portions of 64 tokens and more at offsets
+    that are ragged against the 128-row tiles, the pages and the key tiles, beside shorter
+    portions and single tokens."""
     gen = torch.Generator().manual_seed(31)
     q_lens = [300, 1, 129, 2, 128, 1, 65, 700]
     pos0 = [0, 500, 1000, 31, 64, 0, 77, 5]
-    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16)
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16, late_spike=late_spike)
     args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
                 max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
     want = ref.paged_attention(*tensors, **args)
     assert ops.use_tcgen05_attention
-    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    ops.tcgen05_attention_form = form
+    try:
+        got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    finally:
+        ops.tcgen05_attention_form = 0
     ops.check_device_errors()
     _close(got, want, torch.bfloat16, scale=2.0)
     ops.use_tcgen05_attention = False
