@@ -517,7 +517,15 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = instruction_descriptor(BM, PBN);
-      int it = 0, local = 0;
+      // This one thread's instruction stream paces the tensor core (four MMAs of a k-block run
+      // about as long as issuing them takes), so it is kept short: the stage index and its
+      // phase are counted, not divided out, and the operand descriptors of a stage are the
+      // first stage's plus a multiple of the stage size in the address field (bits 0-13, in
+      // units of 16 bytes; the stages lie below 256 KB, so nothing carries out of the field).
+      const uint64_t a_desc0 = smem_descriptor(base);
+      const uint64_t b_desc0 = smem_descriptor(base + P_A_BYTES);
+      int local = 0, s = 0;
+      uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1, use = local >> 1;
@@ -525,18 +533,21 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * ACC;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int s = it % PSTAGES;
-          ok = mbar_wait(full_bar(s), (it / PSTAGES) & 1, abort_flag, p.error, 2);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_try_wait(full_bar(s), phase)) ok = mbar_wait(full_bar(s), phase, abort_flag, p.error, 2);
           if (!ok) break;
           tcgen05_fence_after();
-          const uint32_t a_addr = base + s * P_STAGE_BYTES;
-          const uint32_t b_addr = a_addr + P_A_BYTES;
+          const uint64_t stage_offset = (uint64_t)(uint32_t)(s * (P_STAGE_BYTES >> 4));
+          const uint64_t a_desc = a_desc0 + stage_offset, b_desc = b_desc0 + stage_offset;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_acc, smem_descriptor(a_addr + k * UMMA_K * 2), smem_descriptor(b_addr + k * UMMA_K * 2), idesc,
+            umma_bf16(tmem_acc, a_desc + (uint64_t)(k * UMMA_K * 2 >> 4), b_desc + (uint64_t)(k * UMMA_K * 2 >> 4), idesc,
                       (kb > 0 || k > 0) ? 1u : 0u);
           tcgen05_commit(empty_bar(s));
+          if (++s == PSTAGES) {
+            s = 0;
+            phase ^= 1u;
+          }
         }
         if (ok) tcgen05_commit(tmem_full_bar(acc));
       }
