@@ -53,6 +53,14 @@ struct Params {
   int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
   int out_f32;
   int swiglu;        // NORMAL only: columns come in blocks of 16 gate, 16 up; out[row, n / 2] = silu(gate) * up
+  // q|k|v with rotation and page write in the epilogue (NORMAL, many tokens): out is
+  // qkv [tokens, (heads + 2 kv_heads) d]; a tile of 256 columns holds whole heads.
+  int rotary;
+  const float* rotary_table;   // [tokens, d]: cos of the d/2 frequencies, then sin; or null
+  const int* slots;            // [tokens]: page * page_size + offset, negative: no write; or null
+  __nv_bfloat16* keys;         // [pages, kv_heads, page_size, d]
+  __nv_bfloat16* values;
+  int heads, kv_heads, head_dim, page_size;
   int* error;
 };
 
@@ -253,6 +261,60 @@ __device__ __forceinline__ void store_swiglu_chunk(const Params& p, int row, int
   }
   *(uint4*)out = w0;
   *(uint4*)(out + 8) = w1;
+}
+
+
+// q|k|v in the epilogue: 16 columns `lo` of a head's first half and the 16 columns `hi` that
+// stand d/2 further, of token `row`. Bias, rounding to bfloat16, rotation of q and k
+// (engine/model.py:155-161: lo' = lo c - hi s, hi' = hi c + lo s), then qkv and, for k and v,
+// the token's place in its page. The same arithmetic as the stand-alone kernels.
+__device__ __forceinline__ void store_rotary_chunks(const Params& p, int row, int head, int f0, float* lo, float* hi,
+                                                    const float* cs, const float* sn) {
+  const int d = p.head_dim, half = d >> 1;
+  const int col_lo = head * d + f0, col_hi = col_lo + half;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (p.bias != nullptr) {
+      lo[i] += p.bias[col_lo + i];
+      hi[i] += p.bias[col_hi + i];
+    }
+    lo[i] = __bfloat162float(__float2bfloat16_rn(lo[i]));
+    hi[i] = __bfloat162float(__float2bfloat16_rn(hi[i]));
+  }
+  if (p.rotary_table != nullptr && head < p.heads + p.kv_heads) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float new_lo = lo[i] * cs[i] - hi[i] * sn[i];
+      const float new_hi = hi[i] * cs[i] + lo[i] * sn[i];
+      lo[i] = new_lo;
+      hi[i] = new_hi;
+    }
+  }
+  uint4 packed[4];
+  __nv_bfloat162* h2 = (__nv_bfloat162*)packed;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    h2[i] = __floats2bfloat162_rn(lo[2 * i], lo[2 * i + 1]);
+    h2[8 + i] = __floats2bfloat162_rn(hi[2 * i], hi[2 * i + 1]);
+  }
+  __nv_bfloat16* out = (__nv_bfloat16*)p.out + (size_t)row * p.ld_out;
+  *(uint4*)(out + col_lo) = packed[0];
+  *(uint4*)(out + col_lo + 8) = packed[1];
+  *(uint4*)(out + col_hi) = packed[2];
+  *(uint4*)(out + col_hi + 8) = packed[3];
+  if (head >= p.heads && p.slots != nullptr) {
+    const int slot = p.slots[row];
+    if (slot >= 0) {
+      const int page = slot / p.page_size, offset = slot - page * p.page_size;
+      const bool is_key = head < p.heads + p.kv_heads;
+      const int kv_head = is_key ? head - p.heads : head - p.heads - p.kv_heads;
+      __nv_bfloat16* to = (is_key ? p.keys : p.values) + (((size_t)page * p.kv_heads + kv_head) * p.page_size + offset) * d;
+      *(uint4*)(to + f0) = packed[0];
+      *(uint4*)(to + f0 + 8) = packed[1];
+      *(uint4*)(to + half + f0) = packed[2];
+      *(uint4*)(to + half + f0 + 8) = packed[3];
+    }
+  }
 }
 
 template <int BN>
@@ -566,7 +628,33 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
       tcgen05_fence_after();
       const int row = tile_a * BM + row_in_tile;
       const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
-      if (p.swiglu) {
+      if (p.rotary) {
+        // 16 columns of each half of a head at a time; the token's cosines and sines of those
+        // 16 frequencies are read once and serve every head of the tile.
+        const int d = p.head_dim, half = d >> 1;
+#pragma unroll 1
+        for (int f0 = 0; f0 < half; f0 += 16) {
+          float cs[16], sn[16];
+          if (p.rotary_table != nullptr && row < p.rows_a) {
+            const float4* cos4 = (const float4*)(p.rotary_table + (size_t)row * d + f0);
+            const float4* sin4 = (const float4*)(p.rotary_table + (size_t)row * d + half + f0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 c = cos4[q], sv = sin4[q];
+              cs[q * 4] = c.x; cs[q * 4 + 1] = c.y; cs[q * 4 + 2] = c.z; cs[q * 4 + 3] = c.w;
+              sn[q * 4] = sv.x; sn[q * 4 + 1] = sv.y; sn[q * 4 + 2] = sv.z; sn[q * 4 + 3] = sv.w;
+            }
+          }
+#pragma unroll 1
+          for (int head0 = 0; head0 < PBN; head0 += d) {
+            float lo[16], hi[16];
+            tmem_load16(lane_address + head0 + f0, lo);
+            tmem_load16(lane_address + head0 + half + f0, hi);
+            if (row < p.rows_a && tile_b * PBN + head0 < p.rows_b)
+              store_rotary_chunks(p, row, (tile_b * PBN + head0) / d, f0, lo, hi, cs, sn);
+          }
+        }
+      } else if (p.swiglu) {
 #pragma unroll 1
         for (int c0 = 0; c0 < PBN; c0 += 32) {
           float gate[16], up[16];
@@ -711,6 +799,7 @@ int launch_persistent(const Params& p, const void* a, const void* b, int k, cuda
   long best_cost = -1;
   for (int w : widths) {
     if (p.swiglu && w % 32) continue;         // a tile must not cut a gate block from its up block
+    if (p.rotary && w % p.head_dim) continue; // nor a head
     const int tiles = tiles_a * ((p.rows_b + w - 1) / w);
     const long cost = (long)((tiles + sm_count() - 1) / sm_count()) * (w + 32);
     if (best_cost < 0 || cost < best_cost) {
@@ -749,6 +838,46 @@ PAE_EXPORT int pae_linear_swiglu_tcgen05(void* out, const void* x, const void* w
   p.kb_per_split = p.k_blocks;
   p.ld_out = n / 2;
   p.swiglu = 1;
+  p.error = error;
+  return launch_persistent(p, x, w, k, (cudaStream_t)stream);
+}
+
+// 1 when the many-token product can finish q|k|v itself for this head size.
+PAE_EXPORT int pae_linear_rotary_tcgen05_supports(int d) { return d >= 32 && d % 32 == 0 && 256 % d == 0; }
+
+// qkv[tokens, n] = x . w^T + bias with n = (heads + 2 kv_heads) d, q and k rotated by
+// rotary [tokens, d] (or not, when null), and k and v also written to their pages at `slots`
+// (or not, when null): the product, `pae_rotary_qk_cache_write` and the page write in one
+// kernel. Many tokens only (more than 64); head sizes that divide 256.
+PAE_EXPORT int pae_linear_rotary_tcgen05(void* qkv, const void* x, const void* w, const float* bias, const float* rotary,
+                                         const int* slots, void* keys, void* values, int tokens, int heads, int kv_heads,
+                                         int d, int page_size, int k, int* error, void* stream) {
+  const int n = (heads + 2 * kv_heads) * d;
+  if (tokens == 0 || n == 0) return 0;
+  if (!pae_linear_rotary_tcgen05_supports(d)) return fail(2, "linear_rotary_tcgen05: head_dim %d does not divide 256 in steps of 32", d);
+  if (n < 256) return fail(2, "linear_rotary_tcgen05: %d columns are fewer than the 256 of a tile", n);
+  if (slots != nullptr && (keys == nullptr || values == nullptr || page_size < 1))
+    return fail(2, "linear_rotary_tcgen05: slots without pages");
+  if (((uintptr_t)qkv | (uintptr_t)keys | (uintptr_t)values | (uintptr_t)rotary) & 15)
+    return fail(2, "linear_rotary_tcgen05: an operand does not start on a 16-byte boundary");
+  if (int err = check_operands(x, w, k)) return err;
+  Params p{};
+  p.out = qkv;
+  p.bias = bias;
+  p.rows_a = tokens;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = p.k_blocks;
+  p.ld_out = n;
+  p.rotary = 1;
+  p.rotary_table = rotary;
+  p.slots = slots;
+  p.keys = (__nv_bfloat16*)keys;
+  p.values = (__nv_bfloat16*)values;
+  p.heads = heads;
+  p.kv_heads = kv_heads;
+  p.head_dim = d;
+  p.page_size = page_size;
   p.error = error;
   return launch_persistent(p, x, w, k, (cudaStream_t)stream);
 }

@@ -337,6 +337,47 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
     return qkv
 
 
+# Whether q|k|v of a prompt's portion is finished (bias, rotation, page write) by the product's own epilogue.
+fuse_qkv_epilogue = True
+
+
+def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_kv_heads, head_dim, page_size) -> torch.Tensor:
+    """`rotary_qk_cache_write(linear(x, weight, bias), ...)`: q|k|v of the step's tokens, q and k
+    rotated, k and v written to their pages. For more than 64 tokens on the tensor-core path it
+    is one kernel (the product's epilogue rotates and writes); otherwise the two calls, which
+    for few tokens fuse the other way round (the split sum runs inside the rotation kernel)."""
+    m, k = x.shape
+    n = weight.shape[0]
+    if (fuse_qkv_epilogue and m > SWAPPED_MAX_TOKENS and n >= 256 and n == (num_heads + 2 * num_kv_heads) * head_dim
+            and weight.shape[1] == k and not isinstance(x, PendingSum) and _tensor_core_shape(x, weight, None, x.dtype)
+            and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
+        lib = _lib("gemm_tcgen05")
+        if lib.pae_linear_rotary_tcgen05_supports(c_int(head_dim)):
+            _need(x, "qkv_projection: x")
+            _need(weight, "qkv_projection: weight")
+            if bias is not None:
+                _need(bias, "qkv_projection: bias", torch.float32)
+                if bias.numel() != n:
+                    raise KernelError(f"qkv_projection: bias of {bias.numel()} for {n} columns")
+            if table is not None:
+                _need(table, "qkv_projection: table", torch.float32)
+                if tuple(table.shape) != (m, head_dim):
+                    raise KernelError(f"qkv_projection: table is {tuple(table.shape)}, [{m}, {head_dim}] is needed")
+            if slots is not None:
+                _need(slots, "qkv_projection: slots", torch.int32)
+                _need(keys, "qkv_projection: keys", torch.bfloat16)
+                _need(values, "qkv_projection: values", torch.bfloat16)
+            out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+            _check(lib, lib.pae_linear_rotary_tcgen05(
+                _ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(table), _ptr(slots),
+                _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), c_int(m),
+                c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k),
+                _ptr(_error_flag(x.device)), _stream()))
+            return out
+    return rotary_qk_cache_write(linear(x, weight, bias), table, slots, keys, values, num_heads, num_kv_heads, head_dim,
+                                 page_size)
+
+
 def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64, wave_blocks: int = 444) -> tuple[int, int]:
     """(keys per slice, slices) for the decode kernel. A block is four slices of one (request,
     kv head) pair, and `wave_blocks` blocks run at one time: as many slices as keep all blocks

@@ -66,12 +66,17 @@ class GQAAttention(Part):
     def forward(self, ctx, x, residual, cache):
         ops = self.ops
         group = ctx.groups[cache.group]
-        qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
         table = self.position_encoding.table(ctx) if self.position_encoding is not None else None
-        qkv = ops.rotary_qk_cache_write(
-            qkv, table, group.slots if cache.writes else None, cache.keys, cache.values,
-            self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
-        )
+        slots = group.slots if cache.writes else None
+        project = getattr(ops, "qkv_projection", None)
+        if project is not None:          # the product, the rotation and the page write as one call
+            qkv = project(x, self.qkv_weight, self.qkv_bias, table, slots, cache.keys, cache.values,
+                          self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size)
+        else:
+            qkv = ops.rotary_qk_cache_write(
+                ops.linear(x, self.qkv_weight, self.qkv_bias), table, slots, cache.keys, cache.values,
+                self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
+            )
         out = ops.paged_attention(
             qkv, cache.keys, cache.values, group.block_table, ctx.q_start, ctx.q_pos0, ctx.kv_len,
             self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,

@@ -147,3 +147,36 @@ def test_swiglu_inside_the_product(ops, m, inter, k):
     assert (got.float().cpu() - want.float()).abs().max().item() <= limit
     assert (got.float() - apart.float()).abs().max().item() <= limit
     assert ops.interleave_gate_up(gate[:24], up[:24]) is None, "an intermediate size that is no multiple of 16 stays apart"
+
+
+@pytest.mark.parametrize("tokens", [65, 300, 2048])
+@pytest.mark.parametrize("heads,kv_heads,d,page,k", [(12, 2, 128, 16, 1536), (4, 2, 64, 16, 256), (6, 3, 32, 8, 96), (5, 5, 128, 32, 264)])
+def test_qkv_finished_in_the_products_epilogue(ops, tokens, heads, kv_heads, d, page, k):
+    """q|k|v for a prompt's portion: bias, rotation and page write in the epilogue of the product
+    give the same bits as the product followed by the rotation kernel."""
+    width = (heads + 2 * kv_heads) * d
+    x = _rand((tokens, k), 70)
+    w = _rand((width, k), 71, 0.05)
+    bias = torch.randn(width).cuda()
+    positions = torch.arange(11, 11 + tokens, dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, d, 2).float() / d))).cuda()
+    table = ops.rotary_table(positions, inv_freq)
+    pages = -(-tokens // page) + 3
+    slots = torch.randperm(pages * page)[:tokens].to(torch.int32)
+    slots[5] = -1                                    # a token whose page write is switched off
+    slots = slots.cuda()
+    caches = [torch.zeros(pages, kv_heads, page, d, dtype=torch.bfloat16).cuda() for _ in range(4)]
+    before = ops.launches
+    fused = ops.qkv_projection(x, w, bias, table, slots, caches[0], caches[1], heads, kv_heads, d, page)
+    assert ops.launches - before == 1, "one kernel"
+    ops.check_device_errors()
+    ops.fuse_qkv_epilogue = False
+    try:
+        apart = ops.qkv_projection(x, w, bias, table, slots, caches[2], caches[3], heads, kv_heads, d, page)
+    finally:
+        ops.fuse_qkv_epilogue = True
+    assert torch.equal(fused, apart)
+    assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+    # and without a position encoding or pages to write
+    plain = ops.qkv_projection(x, w, bias, None, None, caches[0], caches[1], heads, kv_heads, d, page)
+    assert torch.equal(plain, ops.materialized(ops.linear(x, w, bias)))
