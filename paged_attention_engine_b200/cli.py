@@ -26,7 +26,10 @@ from pathlib import Path
 
 
 def _engine_options(parser: argparse.ArgumentParser) -> None:
-    parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    source = parser.add_mutually_exclusive_group(required=True)
+    source.add_argument("--model", help="folder with config.json and model.safetensors")
+    source.add_argument("--random", metavar="CONFIG", help="a config.json: the model gets random weights (see --weights-seed)")
+    parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random")
     parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
     parser.add_argument("--num-blocks", type=int, default=3584, help="pages of the cache pool (reference: 3584)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per page (reference: 16)")
@@ -38,11 +41,15 @@ def _engine_options(parser: argparse.ArgumentParser) -> None:
 def _llm(args, max_num_seqs=None):
     from .engine.api import LLM
 
-    return LLM.from_pretrained(
-        args.model, dtype=args.dtype, num_blocks=args.num_blocks, block_size=args.block_size,
+    options = dict(
+        dtype=args.dtype, num_blocks=args.num_blocks, block_size=args.block_size,
         max_num_seqs=max_num_seqs or args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
         admission_margin_blocks=args.admission_margin_blocks,
     )
+    if args.random:
+        # the same weights as `random-model --seed` writes for this configuration
+        return LLM.from_random(json.loads(Path(args.random).read_text()), seed=args.weights_seed, as_written=True, **options)
+    return LLM.from_pretrained(args.model, **options)
 
 
 def cmd_generate(args) -> int:

@@ -51,8 +51,9 @@ class LLM:
         return cls(Engine.from_pretrained(folder, dtype, device), **options)
 
     @classmethod
-    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0", **options) -> "LLM":
-        return cls(Engine.from_random(raw_config, seed, dtype, device), **options)
+    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0",
+                    as_written: bool = False, **options) -> "LLM":
+        return cls(Engine.from_random(raw_config, seed, dtype, device, as_written=as_written), **options)
 
     def add_request(self, request: Request) -> bool:
         return self.scheduler.add_request(request)

@@ -68,12 +68,15 @@ class Engine:
         return cls(config, spec, tensors, runtime)
 
     @classmethod
-    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0", ops=None) -> "Engine":
-        """Random weights drawn on the device, without a folder (for measurements of large shapes)."""
+    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0", ops=None,
+                    as_written: bool = False) -> "Engine":
+        """Random weights without a folder. They are drawn on the device (quick at large shapes);
+        with `as_written` on the CPU instead, which gives the very tensors that
+        `write_random_model` writes for this configuration, seed and dtype."""
         dtype = as_dtype(dtype)
         config, spec = resolve(raw_config)
         runtime = Runtime(ops or _default_ops(), dtype, torch.device(device))
-        tensors = random_tensors(raw_config, seed, dtype, runtime.device)
+        tensors = random_tensors(raw_config, seed, dtype, "cpu" if as_written else runtime.device)
         tensors = place_tensors(tensors, spec, dtype, runtime.device, "random weights")
         return cls(config, spec, tensors, runtime)
 

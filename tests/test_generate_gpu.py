@@ -138,3 +138,31 @@ def test_tokens_fed_forward_on_the_device_equal_tokens_read_back(tmp_path_factor
     now, _ = run(False)
     assert late == now
     assert all(len(v) == 30 and min(v) >= 0 for v in late.values())
+
+
+def test_command_line_generates_what_the_entry_point_generates(tmp_path):
+    """`python -m paged_attention_engine_b200 generate`, from a model folder and from a
+    configuration with random weights, prints the tokens that LLM.generate returns."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from paged_attention_engine_b200 import LLM
+
+    raw, page, seed = helpers.TINY["tiny_b"]
+    folder = helpers.write_model(tmp_path / "model", raw, seed, torch.bfloat16)
+    config = tmp_path / "cfg.json"
+    config.write_text(json.dumps(raw))
+    prompts = [helpers.random_tokens(raw["vocab_size"], 21, 5), helpers.random_tokens(raw["vocab_size"], 3, 6)]
+    want = LLM.from_pretrained(folder, dtype="bfloat16", num_blocks=64, block_size=page).generate(prompts, max_new_tokens=9)
+    root = Path(__file__).resolve().parent.parent
+    common = ["--dtype", "bfloat16", "--num-blocks", "64", "--block-size", str(page), "--max-new-tokens", "9"]
+    for p in prompts:
+        common += ["--prompt-ids", ",".join(str(t) for t in p)]
+    for source in (["--model", str(folder)], ["--random", str(config), "--weights-seed", str(seed)]):
+        done = subprocess.run([sys.executable, "-m", "paged_attention_engine_b200", "generate", *source, *common],
+                              cwd=root, capture_output=True, text=True, timeout=600)
+        assert done.returncode == 0, done.stderr[-2000:]
+        rows = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+        assert [tuple(r["token_ids"]) for r in rows] == [tuple(w) for w in want], source
