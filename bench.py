@@ -132,7 +132,7 @@ def standing_requests(runner, cache, batch: int, context: int, vocab: int, torch
     return keys
 
 
-def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampler_cls, sampling_row):
+def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampling_row):
     """Device-timed decode: `warmup` + `steps` steps of `batch` single tokens ending at CONTEXT."""
     from paged_attention_engine_b200.engine.batch import StepEntry
     from paged_attention_engine_b200.kernels import ops
@@ -276,7 +276,7 @@ def main() -> int:
     import torch
 
     from paged_attention_engine_b200.engine.llm import Engine
-    from paged_attention_engine_b200.sampling import Sampler, SamplingRow
+    from paged_attention_engine_b200.sampling import SamplingRow
 
     torch.cuda.set_device(0)
     model = dict(MODEL)
@@ -291,19 +291,19 @@ def main() -> int:
                           "frac": round(flops / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)}))
         return 0
     if args.only == "decode":
-        decode = time_decode(engine, args.batch, args.steps, warmup, torch, Sampler, SamplingRow)
+        decode = time_decode(engine, args.batch, args.steps, warmup, torch, SamplingRow)
         print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(decode["ms_per_step"], 4),
                           "tokens_per_s": round(decode["tokens_per_s"], 1), "launches": decode["launches"]}))
         return 0
 
     sampler = ClockSampler()
     sampler.start()
-    decode = time_decode(engine, args.batch, args.steps, warmup, torch, Sampler, SamplingRow)
+    decode = time_decode(engine, args.batch, args.steps, warmup, torch, SamplingRow)
 
     points = {}
     if not args.skip_points:
         for name, b in (("decode_b1", 1), ("decode_b64", 64)):
-            points[name] = round(time_decode(engine, b, max(8, args.steps // 2), 3, torch, Sampler, SamplingRow)["tokens_per_s"], 1)
+            points[name] = round(time_decode(engine, b, max(8, args.steps // 2), 3, torch, SamplingRow)["tokens_per_s"], 1)
     prefill_ms = time_prefill(engine, torch)
     e2e = time_end_to_end(engine, args.batch, args.steps, warmup, torch)
     clocks = sampler.stop()      # sampled through every timed region of this run

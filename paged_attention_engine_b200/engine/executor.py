@@ -9,7 +9,7 @@ from typing import Hashable, Sequence
 import torch
 
 from ..cache.allocator import AllocResult
-from ..sampling import Sampler, SamplingRow
+from ..sampling import SamplingRow
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import ScheduledWork, WorkResult
@@ -40,7 +40,6 @@ class ModelExecutor:
     def __init__(self, runner: ModelRunner, asynchronous: bool | None = None) -> None:
         self.runner = runner
         self.manager = runner.manager
-        self.sampler = Sampler(runner.runtime.ops, runner.runtime.device)
         on_gpu = runner.runtime.device.type == "cuda"
         self.asynchronous = on_gpu if asynchronous is None else (asynchronous and on_gpu)
         self._host_tokens = [torch.empty(1024, dtype=torch.int32).pin_memory() for _ in range(4)] if on_gpu else []

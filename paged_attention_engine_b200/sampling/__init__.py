@@ -1,3 +1,3 @@
-from .sampler import Sampler, SamplingRow
+from .sampler import SamplingRow
 
-__all__ = ["Sampler", "SamplingRow"]
+__all__ = ["SamplingRow"]
