@@ -10,7 +10,10 @@ PAE_EXPORT int pae_attention_mma_supports(int heads, int kv_heads, int d, int pa
          heads % kv_heads == 0 && heads / kv_heads <= 16;
 }
 
-// How many blocks of the decode kernel (four slices each) the device holds at one time: the
+// How many slices a block of the decode kernel takes.
+PAE_EXPORT int pae_decode_slices_per_block() { return SLICE_WARPS; }
+
+// How many blocks of the decode kernel the device holds at one time: the
 // slicing aims at one such wave, since a second, partly filled one costs as much as a full one.
 PAE_EXPORT int pae_decode_blocks_per_wave(int d) {
   static int cached[3] = {0, 0, 0};
@@ -18,17 +21,17 @@ PAE_EXPORT int pae_decode_blocks_per_wave(int d) {
   if (cached[which] == 0) {
     int device = 0, sms = 148, per_sm = 0;
     if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    const size_t bytes = (size_t)DECODE_WARPS * 4 * TILE_KEYS * (d == 32 ? 32 : (d == 64 ? 64 : 128)) * 2;
+    const size_t bytes = slices_smem_bytes(d == 32 ? 32 : (d == 64 ? 64 : 128));
     cudaError_t err;
     if (d == 32) {
       allow_smem(decode_slices_kernel<32>, bytes, "paged_attention_decode");
-      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<32>, DECODE_WARPS * 32, bytes);
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<32>, SLICE_WARPS * 32, bytes);
     } else if (d == 64) {
       allow_smem(decode_slices_kernel<64>, bytes, "paged_attention_decode");
-      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<64>, DECODE_WARPS * 32, bytes);
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<64>, SLICE_WARPS * 32, bytes);
     } else {
       allow_smem(decode_slices_kernel<128>, bytes, "paged_attention_decode");
-      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<128>, DECODE_WARPS * 32, bytes);
+      err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_slices_kernel<128>, SLICE_WARPS * 32, bytes);
     }
     cached[which] = (err == cudaSuccess && per_sm > 0 ? per_sm : 1) * sms;
   }

@@ -40,6 +40,12 @@ using namespace pae;
 
 constexpr int TILE_KEYS = 16;            // keys per MMA step of the decode kernel: never straddles a page
 constexpr int DECODE_WARPS = 4;
+// The sliced decode kernel: warps (slices) per block, and tiles of 16 keys that a warp keeps in
+// flight. A tile takes about a microsecond to arrive and a slice is a handful of tiles, so a
+// slice's time is its number of tiles divided by the depth, in microseconds; two warps of
+// four stages use the shared memory of four warps of two.
+constexpr int SLICE_WARPS = 2;
+constexpr int SLICE_STAGES = 4;
 constexpr int PREFILL_BQ = 64;           // query tokens per block
 constexpr int PREFILL_BKEYS = 64;        // keys per iteration
 constexpr float LOG2E = 1.4426950408889634f;
@@ -237,15 +243,15 @@ struct DecodeParams {
 };
 
 template <int D>
-__global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(SLICE_WARPS * 32) decode_slices_kernel(const DecodeParams p) {
   // The step's integers (starts, lengths, block tables) were copied in before the step began
   // and the keys and values of EARLIER tokens are not written by any kernel of this step, so
-  // a slice's first tile is fetched before the wait for the kernel that precedes this one
+  // a slice's first tiles are fetched before the wait for the kernel that precedes this one
   // (which writes this step's queries, keys and values). Every block waits before it leaves.
   dependent_launch_trigger();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int slice = blockIdx.x * DECODE_WARPS + warp;
+  const int slice = blockIdx.x * SLICE_WARPS + warp;
   const int g = blockIdx.y, b = blockIdx.z;
   const int token = p.q_start[b];
   const int kv_len = p.kv_len[b];
@@ -261,7 +267,7 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const 
   const int groups = p.heads / p.kv_heads;
   const int row_elems = (p.heads + 2 * p.kv_heads) * D;
   constexpr int TILE_BYTES = TILE_KEYS * D * 2;
-  uint8_t* mine = smem + warp * 4 * TILE_BYTES;             // two stages of (K tile, V tile)
+  uint8_t* mine = smem + warp * SLICE_STAGES * 2 * TILE_BYTES;      // stages of (K tile, V tile)
   const uint32_t mine_u32 = smem_u32(mine);
   const int* table = p.block_table + (size_t)b * p.table_width;
 
@@ -279,28 +285,40 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_slices_kernel(const 
     }
   };
 
-  const bool early = begin + TILE_KEYS <= kv_len - 1;       // the first tile holds earlier tokens only
-  if (early) fetch(0, begin);
+  // Tiles 0 .. SLICE_STAGES - 2 start the pipeline, one commit group each; those that hold
+  // earlier tokens only are asked for before the wait.
+  const int tiles = (end - begin + TILE_KEYS - 1) / TILE_KEYS;
+  int early = 0;
+  while (early < SLICE_STAGES - 1 && early < tiles && begin + (early + 1) * TILE_KEYS <= kv_len - 1) {
+    fetch(early, begin + early * TILE_KEYS);
+    cp_async_commit();
+    ++early;
+  }
   dependent_launch_wait();
   uint32_t q[D / 16][4];
   load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
     return r < groups ? p.qkv + (size_t)token * row_elems + (size_t)(g * groups + r) * D : nullptr;
   });
-  if (!early) fetch(0, begin);
-  cp_async_commit();
+  for (int i = early; i < SLICE_STAGES - 1; ++i) {
+    if (i < tiles) fetch(i, begin + i * TILE_KEYS);
+    cp_async_commit();
+  }
 
   float o[D / 8][4];
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float row_max[2] = {-FLT_MAX, -FLT_MAX}, row_sum[2] = {0.f, 0.f};
 
-  const int tiles = (end - begin + TILE_KEYS - 1) / TILE_KEYS;
   for (int t = 0; t < tiles; ++t) {
-    if (t + 1 < tiles) fetch((t + 1) & 1, begin + (t + 1) * TILE_KEYS);
+    // The stage that tile t + SLICE_STAGES - 1 goes to held tile t - 1, which is read (the
+    // __syncwarp that ends every round). One commit group per round, empty or not, so that
+    // "all but the newest SLICE_STAGES - 1 groups" always means "tile t has arrived".
+    const int ahead = t + SLICE_STAGES - 1;
+    if (ahead < tiles) fetch(ahead % SLICE_STAGES, begin + ahead * TILE_KEYS);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<SLICE_STAGES - 1>();
     __syncwarp();
-    const uint32_t k_tile = mine_u32 + (t & 1) * 2 * TILE_BYTES;
+    const uint32_t k_tile = mine_u32 + (t % SLICE_STAGES) * 2 * TILE_BYTES;
     const int key0 = begin + t * TILE_KEYS;
     float s[2][4];
     scores_16_keys<D>(s, q, k_tile, 0);
@@ -457,17 +475,23 @@ __global__ void __launch_bounds__(DECODE_WARPS * 32) decode_cluster_kernel(const
 }
 
 // out[token, head, :] = sum_s w_s part_out[s] / sum_s w_s part_sum[s], w_s = 2^(max_s - max).
-// One block per (request, head): the weights of all slices are worked out once, in parallel,
-// into shared memory; then every thread owns one output dimension and folds the slices in
-// their order with independent loads.
+// One block of four warps per (request, head). Everything the block needs is asked for before
+// anything is waited for: a thread's slice maxima and sums, and the partial outputs of the
+// slices its warp folds (warp w takes slices w, w + 4, ...; a lane owns D / 32 neighbouring
+// dimensions), sixteen slices per warp at a time. The weights are then worked out once into
+// shared memory, each warp folds its slices in their order, and the warps' sums are added in
+// the order of the warps, so the result does not depend on timing.
+constexpr int MERGE_WARPS = 4;
+constexpr int MERGE_DEPTH = 16;      // slices per warp whose partial outputs are in registers at one time
+
 template <int D>
-__global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_out,
-                                    const float* __restrict__ part_max, const float* __restrict__ part_sum,
-                                    const int* __restrict__ q_start, const int* __restrict__ kv_len, int heads, int window,
-                                    int slice_keys, int max_slices) {
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_slices_kernel(
+    __nv_bfloat16* __restrict__ out, const float* __restrict__ part_out, const float* __restrict__ part_max,
+    const float* __restrict__ part_sum, const int* __restrict__ q_start, const int* __restrict__ kv_len, int heads, int window,
+    int slice_keys, int max_slices) {
   dependent_launch_prologue();
-  extern __shared__ float weights[];          // [max_slices]
-  __shared__ float reduce[32];
+  extern __shared__ float weights[];          // [max_slices], then [MERGE_WARPS][D]
+  __shared__ float reduce[2 * MERGE_WARPS];
   const int h = blockIdx.x, b = blockIdx.y;
   const int token = q_start[b];
   if (q_start[b + 1] - token != 1) return;
@@ -476,8 +500,27 @@ __global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float
   const int base = (first_key / TILE_KEYS) * TILE_KEYS;
   const int slices = min(max_slices, (n_kv - base + slice_keys - 1) / slice_keys);
   const size_t at = ((size_t)b * heads + h) * max_slices;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int PER_LANE = D / 32;
 
+  // ---- requests: this warp's first MERGE_DEPTH partial outputs, then the maxima and sums
+  float part[MERGE_DEPTH][PER_LANE];
+#pragma unroll
+  for (int i = 0; i < MERGE_DEPTH; ++i) {
+    const int s = warp + i * MERGE_WARPS;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) part[i][j] = 0.f;
+    if (s < slices) {
+      const float* from = part_out + (at + s) * D + lane * PER_LANE;
+      if (PER_LANE == 4) {
+        const float4 v = *(const float4*)from;
+        part[i][0] = v.x; part[i][1] = v.y; part[i][2] = v.z; part[i][3] = v.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < PER_LANE; ++j) part[i][j] = from[j];
+      }
+    }
+  }
   float top = -FLT_MAX;
   for (int s = threadIdx.x; s < slices; s += blockDim.x) {
     const float m = part_max[at + s];
@@ -489,48 +532,50 @@ __global__ void merge_slices_kernel(__nv_bfloat16* __restrict__ out, const float
   if (lane == 0) reduce[warp] = top;
   __syncthreads();
   top = reduce[0];
-  for (int w = 1; w < warps; ++w) top = fmaxf(top, reduce[w]);
-  __syncthreads();
+#pragma unroll
+  for (int w = 1; w < MERGE_WARPS; ++w) top = fmaxf(top, reduce[w]);
 
   float total = 0.f;
   for (int s = threadIdx.x; s < slices; s += blockDim.x) {
-    const float w = exp2f(weights[s] - top);
+    const float w = exp2f(weights[s] - top);    // this thread wrote weights[s] itself
     weights[s] = w;
     total += part_sum[at + s] * w;
   }
   total = warp_sum(total);
-  if (lane == 0) reduce[warp] = total;
-  __syncthreads();
+  if (lane == 0) reduce[MERGE_WARPS + warp] = total;
+  __syncthreads();                              // the weights of all slices and the warps' sums are in place
   total = 0.f;
-  for (int w = 0; w < warps; ++w) total += reduce[w];
+#pragma unroll
+  for (int w = 0; w < MERGE_WARPS; ++w) total += reduce[MERGE_WARPS + w];
   const float inv = total > 0.f ? 1.f / total : 0.f;
 
-  __syncthreads();      // `reduce` is read above and reused below
-  // Warp w folds slices w, w + warps, ...; a lane owns D / 32 neighbouring dimensions. The
-  // warps' sums are then added in the order of the warps, so the result does not depend on timing.
-  constexpr int PER_LANE = D / 32;
+  // ---- this warp's slices in their order
   float acc[PER_LANE];
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) acc[j] = 0.f;
-#pragma unroll 4
-  for (int s = warp; s < slices; s += warps) {
-    const float w = weights[s];
-    const float* from = part_out + (at + s) * D + lane * PER_LANE;
-    if (PER_LANE == 4) {
-      const float4 p = *(const float4*)from;
-      acc[0] += p.x * w; acc[1] += p.y * w; acc[2] += p.z * w; acc[3] += p.w * w;
-    } else {
 #pragma unroll
-      for (int j = 0; j < PER_LANE; ++j) acc[j] += from[j] * w;
+  for (int i = 0; i < MERGE_DEPTH; ++i) {
+    const int s = warp + i * MERGE_WARPS;
+    if (s < slices) {
+      const float w = weights[s];
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) acc[j] += part[i][j] * w;
     }
   }
-  float* across = weights + max_slices;          // [warps][D]
+  for (int s = warp + MERGE_DEPTH * MERGE_WARPS; s < slices; s += MERGE_WARPS) {     // more than 64 slices
+    const float w = weights[s];
+    const float* from = part_out + (at + s) * D + lane * PER_LANE;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) acc[j] += from[j] * w;
+  }
+  float* across = weights + max_slices;          // [MERGE_WARPS][D]
 #pragma unroll
   for (int j = 0; j < PER_LANE; ++j) across[warp * D + lane * PER_LANE + j] = acc[j];
   __syncthreads();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = 0.f;
-    for (int w = 0; w < warps; ++w) v += across[w * D + d];
+#pragma unroll
+    for (int w = 0; w < MERGE_WARPS; ++w) v += across[w * D + d];
     out[((size_t)token * heads + h) * D + d] = __float2bfloat16_rn(v * inv);
   }
 }
@@ -693,15 +738,17 @@ int allow_smem(Kernel kernel, size_t bytes, const char* what) {
   return 0;
 }
 
+inline size_t slices_smem_bytes(int d) { return (size_t)SLICE_WARPS * SLICE_STAGES * 2 * TILE_KEYS * d * 2; }
+
 template <int D>
 int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int seqs, cudaStream_t s) {
-  const size_t bytes = (size_t)DECODE_WARPS * 4 * TILE_KEYS * D * 2;
+  const size_t bytes = slices_smem_bytes(D);
   if (int err = allow_smem(decode_slices_kernel<D>, bytes, "paged_attention_decode")) return err;
-  dim3 grid((p.max_slices + DECODE_WARPS - 1) / DECODE_WARPS, p.kv_heads, seqs);
-  launch_kernel(decode_slices_kernel<D>, grid, DECODE_WARPS * 32, bytes, s, p);
+  dim3 grid((p.max_slices + SLICE_WARPS - 1) / SLICE_WARPS, p.kv_heads, seqs);
+  launch_kernel(decode_slices_kernel<D>, grid, SLICE_WARPS * 32, bytes, s, p);
   if (int err = check_launch("paged_attention_decode")) return err;
   if ((size_t)(p.max_slices + 4 * D) * sizeof(float) > 40 * 1024) return fail(2, "paged_attention_decode: %d slices are more than the merge takes", p.max_slices);
-  launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), 128, (p.max_slices + 4 * D) * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
+  launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), MERGE_WARPS * 32, (p.max_slices + MERGE_WARPS * D) * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
                                                                      p.kv_len, p.heads, p.window, p.slice_keys, p.max_slices);
   return check_launch("paged_attention_merge");
 }

@@ -378,14 +378,15 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
                                  page_size)
 
 
-def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64, wave_blocks: int = 444) -> tuple[int, int]:
-    """(keys per slice, slices) for the decode kernel. A block is four slices of one (request,
-    kv head) pair, and `wave_blocks` blocks run at one time: as many slices as keep all blocks
-    in that one wave (a second, partly filled wave costs as much as a full one), at most
-    `most`, each of at least 32 keys in steps of 16."""
+def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64, wave_blocks: int = 444,
+                   slices_per_block: int = 4) -> tuple[int, int]:
+    """(keys per slice, slices) for the decode kernel. A block is `slices_per_block` slices of
+    one (request, kv head) pair, and `wave_blocks` blocks run at one time: as many slices as
+    keep all blocks in that one wave (a second, partly filled wave costs as much as a full
+    one), at most `most`, each of at least 32 keys in steps of 16."""
     pairs = max(1, seqs * kv_heads)
     blocks_per_pair = max(1, wave_blocks // pairs)
-    wanted = max(1, min(most, 4 * blocks_per_pair))
+    wanted = max(1, min(most, slices_per_block * blocks_per_pair))
     slice_keys = max(32, -(-(-(-max_kv_len // wanted)) // 16) * 16)
     while -(-(max_kv_len + 15) // slice_keys) > wanted:
         slice_keys += 16
@@ -418,7 +419,8 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
         launches = 1
     else:
         wave = lib.pae_decode_blocks_per_wave(c_int(head_dim))
-        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave)
+        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave,
+                                                slices_per_block=lib.pae_decode_slices_per_block())
         floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
         scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
         launches = 2
