@@ -19,10 +19,26 @@ using namespace pae;
 
 namespace {
 
+// The sum of a column over the splits, in their order; the loads of twelve splits (then four,
+// then one) are in flight together, so that a sum costs a trip or two to the L2, not one per split.
 __device__ __forceinline__ float split_sum(const float* __restrict__ partial, int splits, size_t plane, size_t at) {
   float v = 0.f;
-#pragma unroll 4
-  for (int s = 0; s < splits; ++s) v += partial[(size_t)s * plane + at];
+  int s = 0;
+  for (; s + 12 <= splits; s += 12) {
+    float p[12];
+#pragma unroll
+    for (int j = 0; j < 12; ++j) p[j] = partial[(size_t)(s + j) * plane + at];
+#pragma unroll
+    for (int j = 0; j < 12; ++j) v += p[j];
+  }
+  for (; s + 4 <= splits; s += 4) {
+    float p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) p[j] = partial[(size_t)(s + j) * plane + at];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v += p[j];
+  }
+  for (; s < splits; ++s) v += partial[(size_t)s * plane + at];
   return v;
 }
 
@@ -65,7 +81,7 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_kernel(T* __restrict__ no
 }
 
 // The same with four columns per thread (rows whose width is a multiple of 4): 16-byte loads
-// of the partial sums, eight splits in flight at a time. Sums run in the order of the splits,
+// of the partial sums, twelve splits in flight at a time. Sums run in the order of the splits,
 // as above, so the rounded value is the same bits; the sum of squares adds four columns per
 // thread first, which may differ from the scalar kernel in the last bit of the norm.
 template <typename T>
@@ -84,12 +100,21 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
     const size_t at4 = (size_t)row * (width / 4) + c;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     int s = 0;
-    for (; s + 8 <= splits; s += 8) {
-      float4 p[8];
+    for (; s + 12 <= splits; s += 12) {
+      float4 p[12];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) p[j] = part4[(size_t)(s + j) * plane4 + at4];
+      for (int j = 0; j < 12; ++j) p[j] = part4[(size_t)(s + j) * plane4 + at4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 12; ++j) {
+        v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w;
+      }
+    }
+    for (; s + 4 <= splits; s += 4) {
+      float4 p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p[j] = part4[(size_t)(s + j) * plane4 + at4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
         v.x += p[j].x; v.y += p[j].y; v.z += p[j].z; v.w += p[j].w;
       }
     }
