@@ -80,24 +80,55 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_kernel(T* __restrict__ no
     normed[(size_t)row * width + i] = from_float<T>(row_values[i] * scale * weight[i]);
 }
 
-// The same with four columns per thread (rows whose width is a multiple of 4): 16-byte loads
-// of the partial sums, twelve splits in flight at a time. Sums run in the order of the splits,
-// as above, so the rounded value is the same bits; the sum of squares adds four columns per
-// thread first, which may differ from the scalar kernel in the last bit of the norm.
+// Four neighbouring values of T as floats, and back (16- or 8-byte accesses).
+__device__ __forceinline__ void load4(const float* p, float* v) {
+  const float4 t = *(const float4*)p;
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float* v) {
+  const uint2 t = *(const uint2*)p;
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&t.x), b = __bfloat1622float2(*(const __nv_bfloat162*)&t.y);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float* v) { *(float4*)p = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
+  uint2 t;
+  *(__nv_bfloat162*)&t.x = __floats2bfloat162_rn(v[0], v[1]);
+  *(__nv_bfloat162*)&t.y = __floats2bfloat162_rn(v[2], v[3]);
+  *(uint2*)p = t;
+}
+
+// The same with four columns per thread (rows whose width is a multiple of 4 and tensors that
+// start on 16 bytes): 16-byte loads of the partial sums, twelve splits in flight at a time. Sums
+// run in the order of the splits, as above, so the rounded value is the same bits; the sum of
+// squares adds four columns per thread first, which may differ from the scalar kernel in the
+// last bit of the norm. The norm's weight and the bias never change during a step: a thread
+// reads those of its first four columns before it waits for the kernel before it, and keeps
+// the values of those columns in registers from the sum to the scaling.
 template <typename T>
 __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__ normed, T* __restrict__ value,
                                                                  const float* __restrict__ partial, int splits,
                                                                  const float* __restrict__ bias, const T* __restrict__ residual,
                                                                  const float* __restrict__ weight, int rows, int width, float eps) {
-  dependent_launch_prologue();
+  dependent_launch_trigger();
+  const int quads = width / 4;
+  float w_first[4] = {0.f, 0.f, 0.f, 0.f}, b_first[4] = {0.f, 0.f, 0.f, 0.f};
+  if ((int)threadIdx.x < quads) {
+    load4(weight + 4 * threadIdx.x, w_first);
+    if (bias != nullptr) load4(bias + 4 * threadIdx.x, b_first);
+  }
+  dependent_launch_wait();
   extern __shared__ float row_values[];
   __shared__ float reduce[32];
   const int row = blockIdx.x;
-  const size_t plane4 = (size_t)rows * width / 4;
+  const size_t plane4 = (size_t)rows * quads;
   const float4* part4 = (const float4*)partial;
   float squares = 0.f;
-  for (int c = threadIdx.x; c < width / 4; c += blockDim.x) {
-    const size_t at4 = (size_t)row * (width / 4) + c;
+  float first[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int c = threadIdx.x; c < quads; c += blockDim.x) {
+    const size_t at4 = (size_t)row * quads + c;
+    float res[4] = {0.f, 0.f, 0.f, 0.f};
+    if (residual != nullptr) load4(residual + (size_t)row * width + 4 * c, res);
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     int s = 0;
     for (; s + 12 <= splits; s += 12) {
@@ -123,16 +154,21 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
       v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
     }
     float e[4] = {v.x, v.y, v.z, v.w};
+    const bool is_first = c == (int)threadIdx.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int i = c * 4 + j;
-      if (bias != nullptr) e[j] += bias[i];
-      if (residual != nullptr) e[j] += to_float(residual[(size_t)row * width + i]);
-      const T rounded = from_float<T>(e[j]);
-      value[(size_t)row * width + i] = rounded;
-      const float r = to_float(rounded);
-      row_values[i] = r;
-      squares += r * r;
+      if (bias != nullptr) e[j] += is_first ? b_first[j] : bias[4 * c + j];
+      if (residual != nullptr) e[j] += res[j];
+      e[j] = to_float(from_float<T>(e[j]));
+      squares += e[j] * e[j];
+    }
+    store4(value + (size_t)row * width + 4 * c, e);
+    if (is_first) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) first[j] = e[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) row_values[4 * c + j] = e[j];
     }
   }
   squares = warp_sum(squares);
@@ -146,7 +182,13 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
   }
   __syncthreads();
   const float scale = reduce[0];
-  for (int i = threadIdx.x; i < width; i += blockDim.x)
+  if ((int)threadIdx.x < quads) {
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = first[j] * scale * w_first[j];
+    store4(normed + (size_t)row * width + 4 * threadIdx.x, o);
+  }
+  for (int i = 4 * blockDim.x + threadIdx.x; i < width; i += blockDim.x)      // rows wider than four columns a thread
     normed[(size_t)row * width + i] = from_float<T>(row_values[i] * scale * weight[i]);
 }
 
@@ -175,37 +217,43 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
                                                  const float* __restrict__ bias, const float* __restrict__ table,
                                                  const int* __restrict__ slots, T* __restrict__ keys, T* __restrict__ values,
                                                  int tokens, int heads, int kv_heads, int d, int page_size) {
-  dependent_launch_prologue();
+  // The bias never changes and the slots were copied in before the step began: both are read
+  // before the wait for the product whose sums this kernel finishes.
+  dependent_launch_trigger();
   const int half = d >> 1;
   const int all_heads = heads + 2 * kv_heads;
   const int per_token = all_heads * half;
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)tokens * per_token) return;
-  const int t = (int)(i / per_token);
-  const int rest = (int)(i - (long long)t * per_token);
+  const bool mine = i < (long long)tokens * per_token;
+  const int t = mine ? (int)(i / per_token) : 0;
+  const int rest = mine ? (int)(i - (long long)t * per_token) : 0;
   const int head = rest / half, f = rest - head * half;
+  const bool to_page = mine && head >= heads && slots != nullptr;
+  const int slot = to_page ? slots[t] : -1;
+  float bias_lo = 0.f, bias_hi = 0.f;
+  if (mine && bias != nullptr) {
+    bias_lo = bias[head * d + f];
+    bias_hi = bias[head * d + f + half];
+  }
+  dependent_launch_wait();
+  if (!mine) return;
   const size_t plane = (size_t)tokens * all_heads * d;
   const size_t at = ((size_t)t * all_heads + head) * d;
+  const bool rotate = head < heads + kv_heads && table != nullptr;
+  const float c = rotate ? table[(size_t)t * d + f] : 1.f, sn = rotate ? table[(size_t)t * d + half + f] : 0.f;
   float lo = split_sum(partial, splits, plane, at + f);
   float hi = split_sum(partial, splits, plane, at + f + half);
-  if (bias != nullptr) {
-    lo += bias[head * d + f];
-    hi += bias[head * d + f + half];
-  }
-  lo = to_float(from_float<T>(lo));
-  hi = to_float(from_float<T>(hi));
-  if (head < heads + kv_heads && table != nullptr) {
-    const float c = table[(size_t)t * d + f], s = table[(size_t)t * d + half + f];
-    const float new_lo = lo * c - hi * s;
-    const float new_hi = hi * c + lo * s;
+  lo = to_float(from_float<T>(lo + bias_lo));
+  hi = to_float(from_float<T>(hi + bias_hi));
+  if (rotate) {
+    const float new_lo = lo * c - hi * sn;
+    const float new_hi = hi * c + lo * sn;
     lo = new_lo;
     hi = new_hi;
   }
   qkv[at + f] = from_float<T>(lo);
   qkv[at + f + half] = from_float<T>(hi);
-  if (head >= heads && slots != nullptr) {
-    const int slot = slots[t];
-    if (slot < 0) return;
+  if (slot >= 0) {
     const int page = slot / page_size, offset = slot - page * page_size;
     const bool is_key = head < heads + kv_heads;
     const int kv_head = is_key ? head - heads : head - heads - kv_heads;
@@ -225,7 +273,8 @@ PAE_EXPORT int pae_splitk_rms_norm(void* normed, void* value, const float* parti
   cudaStream_t s = (cudaStream_t)stream;
   const size_t bytes = (size_t)width * sizeof(float);
   const int threads = width >= 2048 ? 512 : (width >= 512 ? 384 : (width >= 256 ? 128 : 64));
-  const bool by_four = width % 4 == 0 && ((uintptr_t)partial & 15) == 0;
+  const bool by_four = width % 4 == 0 && (((uintptr_t)partial | (uintptr_t)normed | (uintptr_t)value | (uintptr_t)residual |
+                                            (uintptr_t)weight | (uintptr_t)bias) & 15) == 0;
   if (dtype == kBF16) {
     auto kernel = by_four ? splitk_rms_norm_x4_kernel<__nv_bfloat16> : splitk_rms_norm_kernel<__nv_bfloat16>;
     if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
