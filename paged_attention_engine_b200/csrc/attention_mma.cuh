@@ -489,13 +489,17 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_slices_kernel(
     __nv_bfloat16* __restrict__ out, const float* __restrict__ part_out, const float* __restrict__ part_max,
     const float* __restrict__ part_sum, const int* __restrict__ q_start, const int* __restrict__ kv_len, int heads, int window,
     int slice_keys, int max_slices) {
-  dependent_launch_prologue();
+  // The step's integers were copied in before the step began: they are read before the wait
+  // for the kernel that writes the slices.
+  dependent_launch_trigger();
   extern __shared__ float weights[];          // [max_slices], then [MERGE_WARPS][D]
   __shared__ float reduce[2 * MERGE_WARPS];
   const int h = blockIdx.x, b = blockIdx.y;
   const int token = q_start[b];
-  if (q_start[b + 1] - token != 1) return;
+  const bool single = q_start[b + 1] - token == 1;
   const int n_kv = kv_len[b];
+  dependent_launch_wait();
+  if (!single) return;
   const int first_key = window > 0 ? max(0, n_kv - window) : 0;
   const int base = (first_key / TILE_KEYS) * TILE_KEYS;
   const int slices = min(max_slices, (n_kv - base + slice_keys - 1) / slice_keys);

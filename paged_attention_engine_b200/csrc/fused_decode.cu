@@ -175,13 +175,9 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   if (lane == 0) reduce[warp] = squares;
   __syncthreads();
-  if (warp == 0) {
-    float v = lane < warps ? reduce[lane] : 0.f;
-    v = warp_sum(v);
-    if (lane == 0) reduce[0] = rsqrtf(v / (float)width + eps);
-  }
-  __syncthreads();
-  const float scale = reduce[0];
+  float total = 0.f;                            // every thread adds the warps' sums in the warps' order
+  for (int w = 0; w < warps; ++w) total += reduce[w];
+  const float scale = rsqrtf(total / (float)width + eps);
   if ((int)threadIdx.x < quads) {
     float o[4];
 #pragma unroll
