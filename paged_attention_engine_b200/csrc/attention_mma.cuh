@@ -489,8 +489,8 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_slices_kernel(
     __nv_bfloat16* __restrict__ out, const float* __restrict__ part_out, const float* __restrict__ part_max,
     const float* __restrict__ part_sum, const int* __restrict__ q_start, const int* __restrict__ kv_len, int heads, int window,
     int slice_keys, int max_slices) {
-  // The step's integers were copied in before the step began: they are read before the wait
-  // for the kernel that writes the slices.
+  // The kernel before this one is the sliced decode kernel of the same call, which has read
+  // the step's integers itself: they are read before the wait.
   dependent_launch_trigger();
   extern __shared__ float weights[];          // [max_slices], then [MERGE_WARPS][D]
   __shared__ float reduce[2 * MERGE_WARPS];

@@ -80,6 +80,8 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_kernel(T* __restrict__ no
     normed[(size_t)row * width + i] = from_float<T>(row_values[i] * scale * weight[i]);
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 // Four neighbouring values of T as floats, and back (16- or 8-byte accesses).
 __device__ __forceinline__ void load4(const float* p, float* v) {
   const float4 t = *(const float4*)p;
@@ -102,22 +104,30 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
 // start on 16 bytes): 16-byte loads of the partial sums, twelve splits in flight at a time. Sums
 // run in the order of the splits, as above, so the rounded value is the same bits; the sum of
 // squares adds four columns per thread first, which may differ from the scalar kernel in the
-// last bit of the norm. The norm's weight and the bias never change during a step: a thread
-// reads those of its first four columns before it waits for the kernel before it, and keeps
-// the values of those columns in registers from the sum to the scaling.
+// last bit of the norm. A thread asks for the norm's weight and the bias of its first four
+// columns together with the partial sums, and keeps the values of those columns in registers
+// from the sum to the scaling, so nothing is read after the sum of squares is known.
 template <typename T>
 __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__ normed, T* __restrict__ value,
                                                                  const float* __restrict__ partial, int splits,
                                                                  const float* __restrict__ bias, const T* __restrict__ residual,
                                                                  const float* __restrict__ weight, int rows, int width, float eps) {
+  // Before the wait for the kernel before, only hints: the norm's weight is read once a step,
+  // so it comes from DRAM; asking the L2 for it now makes the read below a hit. (A read here
+  // would be unsafe in general: a copy into the tensor that was queued between the kernel
+  // before and this one may not have happened yet.)
   dependent_launch_trigger();
   const int quads = width / 4;
+  if ((int)threadIdx.x < quads && (threadIdx.x & 7) == 0) {
+    prefetch_l2(weight + 4 * threadIdx.x);
+    if (bias != nullptr) prefetch_l2(bias + 4 * threadIdx.x);
+  }
+  dependent_launch_wait();
   float w_first[4] = {0.f, 0.f, 0.f, 0.f}, b_first[4] = {0.f, 0.f, 0.f, 0.f};
-  if ((int)threadIdx.x < quads) {
+  if ((int)threadIdx.x < quads) {               // asked for together with the sums below, used after them
     load4(weight + 4 * threadIdx.x, w_first);
     if (bias != nullptr) load4(bias + 4 * threadIdx.x, b_first);
   }
-  dependent_launch_wait();
   extern __shared__ float row_values[];
   __shared__ float reduce[32];
   const int row = blockIdx.x;
@@ -213,9 +223,7 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
                                                  const float* __restrict__ bias, const float* __restrict__ table,
                                                  const int* __restrict__ slots, T* __restrict__ keys, T* __restrict__ values,
                                                  int tokens, int heads, int kv_heads, int d, int page_size) {
-  // The bias never changes and the slots were copied in before the step began: both are read
-  // before the wait for the product whose sums this kernel finishes.
-  dependent_launch_trigger();
+  dependent_launch_prologue();
   const int half = d >> 1;
   const int all_heads = heads + 2 * kv_heads;
   const int per_token = all_heads * half;
@@ -231,8 +239,8 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
     bias_lo = bias[head * d + f];
     bias_hi = bias[head * d + f + half];
   }
-  dependent_launch_wait();
   if (!mine) return;
+  // Everything is asked for before the sums are waited for: bias, angle, slot.
   const size_t plane = (size_t)tokens * all_heads * d;
   const size_t at = ((size_t)t * all_heads + head) * d;
   const bool rotate = head < heads + kv_heads && table != nullptr;

@@ -63,6 +63,8 @@ class DecoderModel:
             hidden = layer.block.forward(ctx, hidden, layer, entry_caches[position])
         if ctx.logit_rows.numel() == 0:
             return None
-        rows = self.ops.gather_rows(hidden, ctx.logit_rows)
+        # A step that wants the logits of all its tokens (decoding) needs no gather, and the final
+        # norm can finish the last product itself.
+        rows = hidden if getattr(ctx, "wants_every_token", False) else self.ops.gather_rows(hidden, ctx.logit_rows)
         # The head's product may still be waiting for its sum (a step of few wanted rows): logits leave as a tensor.
         return self.ops.materialized(self.head.forward(ctx, self.final_norm.forward(ctx, rows)))
