@@ -132,12 +132,21 @@ __global__ void rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
   const int chunks = width >> 3;
   const uint4* row = (const uint4*)(x + (size_t)blockIdx.x * width);
   uint4 held[PER_THREAD];
+  float4 w0[PER_THREAD], w1[PER_THREAD];        // the weight is asked for with the row, not after the sum
   float sum = 0.f;
 #pragma unroll
   for (int j = 0; j < PER_THREAD; ++j) {
     const int c = threadIdx.x + j * blockDim.x;
     if (c < chunks) {
       held[j] = row[c];
+      w0[j] = *(const float4*)(weight + c * 8);
+      w1[j] = *(const float4*)(weight + c * 8 + 4);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER_THREAD; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < chunks) {
       const __nv_bfloat162* h = (const __nv_bfloat162*)&held[j];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -163,14 +172,13 @@ __global__ void rms_norm_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
     const int c = threadIdx.x + j * blockDim.x;
     if (c < chunks) {
       const __nv_bfloat162* h = (const __nv_bfloat162*)&held[j];
-      const float4 w0 = *(const float4*)(weight + c * 8), w1 = *(const float4*)(weight + c * 8 + 4);
       uint4 packed;
       __nv_bfloat162* o = (__nv_bfloat162*)&packed;
       float2 f;
-      f = __bfloat1622float2(h[0]); o[0] = __floats2bfloat162_rn(f.x * scale * w0.x, f.y * scale * w0.y);
-      f = __bfloat1622float2(h[1]); o[1] = __floats2bfloat162_rn(f.x * scale * w0.z, f.y * scale * w0.w);
-      f = __bfloat1622float2(h[2]); o[2] = __floats2bfloat162_rn(f.x * scale * w1.x, f.y * scale * w1.y);
-      f = __bfloat1622float2(h[3]); o[3] = __floats2bfloat162_rn(f.x * scale * w1.z, f.y * scale * w1.w);
+      f = __bfloat1622float2(h[0]); o[0] = __floats2bfloat162_rn(f.x * scale * w0[j].x, f.y * scale * w0[j].y);
+      f = __bfloat1622float2(h[1]); o[1] = __floats2bfloat162_rn(f.x * scale * w0[j].z, f.y * scale * w0[j].w);
+      f = __bfloat1622float2(h[2]); o[2] = __floats2bfloat162_rn(f.x * scale * w1[j].x, f.y * scale * w1[j].y);
+      f = __bfloat1622float2(h[3]); o[3] = __floats2bfloat162_rn(f.x * scale * w1[j].z, f.y * scale * w1[j].w);
       to[c] = packed;
     }
   }
