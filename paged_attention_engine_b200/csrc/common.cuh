@@ -53,6 +53,17 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// One rotation of a pair (engine/model.py:155-161): lo' = lo c - hi s, hi' = hi c + lo s, each
+// product and each sum rounded on its own. Several kernels rotate (stand-alone, inside the sum
+// of a split product, inside a product's epilogue) and must give the same bits; left to the
+// compiler, one kernel would fuse a multiply into the add and another would not.
+__device__ __forceinline__ void rotate_pair(float& lo, float& hi, float c, float s) {
+  const float new_lo = __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, s));
+  const float new_hi = __fadd_rn(__fmul_rn(hi, c), __fmul_rn(lo, s));
+  lo = new_lo;
+  hi = new_hi;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -261,10 +261,7 @@ __global__ void rotary_qk_cache_write_kernel(T* __restrict__ qkv, const float* _
   float lo = to_float(at[f]), hi = to_float(at[f + half]);
   if (head < heads + kv_heads && table != nullptr) {
     const float c = table[(size_t)t * d + f], s = table[(size_t)t * d + half + f];
-    const float new_lo = lo * c - hi * s;
-    const float new_hi = hi * c + lo * s;
-    lo = new_lo;
-    hi = new_hi;
+    rotate_pair(lo, hi, c, s);
     at[f] = from_float<T>(lo);
     at[f + half] = from_float<T>(hi);
   }

@@ -250,10 +250,7 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
   lo = to_float(from_float<T>(lo + bias_lo));
   hi = to_float(from_float<T>(hi + bias_hi));
   if (rotate) {
-    const float new_lo = lo * c - hi * sn;
-    const float new_hi = hi * c + lo * sn;
-    lo = new_lo;
-    hi = new_hi;
+    rotate_pair(lo, hi, c, sn);
   }
   qkv[at + f] = from_float<T>(lo);
   qkv[at + f + half] = from_float<T>(hi);

@@ -284,10 +284,7 @@ __device__ __forceinline__ void store_rotary_chunks(const Params& p, int row, in
   if (p.rotary_table != nullptr && head < p.heads + p.kv_heads) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float new_lo = lo[i] * cs[i] - hi[i] * sn[i];
-      const float new_hi = hi[i] * cs[i] + lo[i] * sn[i];
-      lo[i] = new_lo;
-      hi[i] = new_hi;
+      rotate_pair(lo[i], hi[i], cs[i], sn[i]);
     }
   }
   uint4 packed[4];

@@ -48,7 +48,9 @@ class _DecodeGraph:
 
 
 class ModelRunner:
-    MAX_GRAPHS = 24
+    # A graph per (batch size, block-table width, sampling). They share one memory pool (they never
+    # run at the same time), so a graph costs its launches and little else.
+    MAX_GRAPHS = 512
 
     def __init__(self, model: DecoderModel, cache: PagedKVCache, use_graphs: bool = True) -> None:
         self.model = model
@@ -61,6 +63,8 @@ class ModelRunner:
         self.entry_caches = [cache.entry_cache(p) for p in range(len(model.spec.schedule))]
         self.use_graphs = use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
         self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self.graph_pool = None
+        self.capture_stream = None
         self.graph_replays = 0
         # The token last sampled for the request in each state slot; a step's token id of -1
         # reads it, so a sampled token can feed the next step without a trip to the host.
@@ -117,14 +121,19 @@ class ModelRunner:
             logits, tokens = slot.logits, slot.tokens
             num_tokens = len(entries)
         elif key is not None and len(self.graphs) < self.MAX_GRAPHS:
-            # First time for this shape: run it eagerly out of the buffer the graph will read
-            # (that is this step's real work), then record the same launches without running them.
+            # First time for this shape: its launches are recorded (nothing runs), then the
+            # recording is replayed, which is this step's real work.
             ctx = self.builder.build(entries, sampling, table_width=key[1])
             slot = _DecodeGraph(ctx.buffer)
+            self._capture(slot, ctx)
             self.graphs[key] = slot
-            logits, tokens = self._run(ctx)
-            num_tokens = ctx.num_tokens
-            self._capture(slot, entries, sampling, key)
+            slot.graph.replay()
+            self.model.forward_pass_count += 1
+            ops = self.runtime.ops
+            if hasattr(ops, "launches"):
+                ops.launches += slot.launches
+            logits, tokens = slot.logits, slot.tokens
+            num_tokens = len(entries)
         else:
             ctx = self.builder.build(entries, sampling)
             logits, tokens = self._run(ctx)
@@ -134,15 +143,28 @@ class ModelRunner:
         wanted = [(e.key, int(w)) for e in entries for w in e.want]
         return StepOutput(logits, wanted, num_tokens, tokens)
 
-    def _capture(self, slot: _DecodeGraph, entries, sampling, key) -> None:
+    def _capture(self, slot: _DecodeGraph, ctx) -> None:
+        """Records the step of `ctx` (whose integers lie in the buffer that replays will refill).
+        The recording runs on a stream of its own, as capture needs, with the graphs' shared pool;
+        torch's context manager is not used because it collects garbage and empties the
+        allocator's cache at every entry, which costs more than the recording."""
         ops = self.runtime.ops
-        torch.cuda.synchronize()
-        ctx = self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer)
         before = getattr(ops, "launches", 0)
-        graph = torch.cuda.CUDAGraph()
         count = self.model.forward_pass_count
-        with torch.cuda.graph(graph):
-            slot.logits, slot.tokens = self._run(ctx)
+        graph = torch.cuda.CUDAGraph()
+        if self.capture_stream is None:
+            self.capture_stream = torch.cuda.Stream(device=self.runtime.device)
+        current = torch.cuda.current_stream(self.runtime.device)
+        self.capture_stream.wait_stream(current)
+        with torch.cuda.stream(self.capture_stream):
+            graph.capture_begin(pool=self.graph_pool)
+            try:
+                slot.logits, slot.tokens = self._run(ctx)
+            finally:
+                graph.capture_end()
+        current.wait_stream(self.capture_stream)
+        if self.graph_pool is None:
+            self.graph_pool = graph.pool()
         self.model.forward_pass_count = count       # recording is not a traversal
         slot.launches = getattr(ops, "launches", 0) - before
         if hasattr(ops, "launches"):

@@ -120,8 +120,15 @@ def test_sum_fused_into_rotation_and_page_write(ops, heads, kv_heads, d, page):
     caches = [torch.zeros(pages, kv_heads, page, d, dtype=torch.bfloat16).cuda() for _ in range(4)]
     fused = ops.rotary_qk_cache_write(pending, table, slots, caches[0], caches[1], heads, kv_heads, d, page)
     unfused = ops.rotary_qk_cache_write(plain.clone(), table, slots, caches[2], caches[3], heads, kv_heads, d, page)
-    assert torch.equal(fused, unfused)
-    assert torch.equal(caches[0], caches[2]) and torch.equal(caches[1], caches[3])
+    def where(a, b):
+        bad = (a != b).nonzero()
+        return f"{bad.shape[0]} of {a.numel()} differ, first at {bad[0].tolist() if bad.shape[0] else None}: " \
+               f"{a[tuple(bad[0])].item() if bad.shape[0] else ''} != {b[tuple(bad[0])].item() if bad.shape[0] else ''}; " \
+               f"pending against plain: {(ops.materialized(pending) != plain).sum().item()} differ"
+
+    assert torch.equal(fused, unfused), "qkv: " + where(fused, unfused)
+    assert torch.equal(caches[0], caches[2]), "keys: " + where(caches[0], caches[2])
+    assert torch.equal(caches[1], caches[3]), "values: " + where(caches[1], caches[3])
 
 
 @pytest.mark.parametrize("m", [1, 8, 64, 65, 300, 2048])
