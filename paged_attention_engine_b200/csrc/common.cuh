@@ -80,13 +80,13 @@ __device__ __forceinline__ float warp_sum(float v) {
 // prologues overlap. A step of decoding is several hundred small kernels; this is worth
 // about a third of its time. PAE_PDL=0 in the environment turns it off.
 //
-// A few kernels do read before the wait. That is sound only for memory that was last written
-// before the kernel BEFORE this one was launched: a copy that was queued between the two
-// kernels may run after this kernel's first instructions. The products read their weights
-// (written when the model was loaded); decode attention reads the step's integers and the
-// keys and values of earlier tokens (written in earlier steps, and by the copy that opens the
-// step, which many kernels follow before the first attention); the merge follows the sliced
-// kernel of the same call. Everything else before a wait is a prefetch hint.
+// A few kernels do read before the wait. The rule they keep: only memory that was last written
+// before the kernel BEFORE this one was launched, which is the only memory certain to be
+// complete at that point whatever the stream did between the two launches. The products read
+// their weights (written when the model was loaded); decode attention reads the step's
+// integers and the keys and values of earlier tokens (written in earlier steps, and by the
+// copy that opens the step, which many kernels follow before the first attention); the merge
+// follows the sliced kernel of the same call. Everything else before a wait is a prefetch hint.
 __device__ __forceinline__ void dependent_launch_prologue() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -114,8 +114,8 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__
                                                                  const float* __restrict__ weight, int rows, int width, float eps) {
   // Before the wait for the kernel before, only hints: the norm's weight is read once a step,
   // so it comes from DRAM; asking the L2 for it now makes the read below a hit. (A read here
-  // would be unsafe in general: a copy into the tensor that was queued between the kernel
-  // before and this one may not have happened yet.)
+  // would need the caller's word that the tensor was written before the kernel before this one
+  // was launched.)
   dependent_launch_trigger();
   const int quads = width / 4;
   if ((int)threadIdx.x < quads && (threadIdx.x & 7) == 0) {
