@@ -27,7 +27,8 @@ class PagedKVCache:
             shape = (len(group.entries), 2, allocator.num_blocks, group.num_kv_heads, self.page_size, group.head_dim)
             self.pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self.states: dict[int, torch.Tensor] = {
-            pos: torch.zeros((manager.slots.num_slots, *need.shape), dtype=need.dtype, device=self.device)
+            # one spare slot behind the real ones, for the padding rows of a captured step
+            pos: torch.zeros((manager.slots.num_slots + 1, *need.shape), dtype=need.dtype, device=self.device)
             for pos, need in plan.state_needs.items()
         }
 

@@ -146,11 +146,16 @@ class BatchBuilder:
         sampling: Sequence[Any] | None = None,
         table_width: int | None = None,
         into: torch.Tensor | None = None,
+        pad_to: int | None = None,
     ) -> StepContext:
         """Flattens the entries. `sampling` (one row per wanted place: temperature, seed,
         request key, output index) travels in the same copy. `table_width` fixes the width of
         the block tables (a captured graph needs the same layout every step) and `into` is
-        the device buffer that such a graph reads."""
+        the device buffer that such a graph reads. `pad_to` (a step of single tokens that wants
+        all their logits only) adds rows up to that many entries: each is a token at position 0
+        of nobody's request, which writes no page (slot -1), reads page 0 and owns the spare
+        state slot behind the real ones; its logits and its token are computed and ignored, so
+        that steps of neighbouring batch sizes can share one captured graph."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         manager = self.manager
@@ -177,12 +182,22 @@ class BatchBuilder:
             pos0.append(start)
             slots_of.append(manager.slot_of(e.key))
 
-        b = len(entries)
+        real = len(entries)
         decode_only = all(n == 1 for n in q_lens)
+        pads = 0
+        if pad_to is not None and pad_to > real:
+            if not decode_only or any(tuple(e.want) != (0,) for e in entries):
+                raise ValueError("only a step of single tokens that wants all their logits can be padded")
+            pads = pad_to - real
+            q_lens = q_lens + [1] * pads
+            pos0 = pos0 + [0] * pads
+            slots_of = slots_of + [manager.slots.num_slots] * pads      # the spare slot behind the real ones
+        b = real + pads
         total = b if decode_only else sum(q_lens)
         pos0_arr = np.asarray(pos0, dtype=np.int32)
         if decode_only:
-            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=b)
+            token_ids = np.zeros(b, dtype=np.int32)
+            token_ids[:real] = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=real)
             seq_index = np.arange(b, dtype=np.int32)
             positions = pos0_arr
             q_start = np.arange(b + 1, dtype=np.int32)
@@ -198,7 +213,7 @@ class BatchBuilder:
         if self.vocab_size is not None and (int(token_ids.min()) < -1 or int(token_ids.max()) >= self.vocab_size):
             bad = int(token_ids[(token_ids < -1) | (token_ids >= self.vocab_size)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
-        rows = [int(q_start[i]) + int(w) for i, e in enumerate(entries) for w in e.want]
+        rows = [int(q_start[i]) + int(w) for i, e in enumerate(entries) for w in e.want] + list(range(real, b))
 
         max_kv = int(kv_len.max())
         width = (max_kv + page - 1) // page
@@ -207,8 +222,8 @@ class BatchBuilder:
                 raise ValueError(f"block tables of {width} pages do not fit the fixed width {table_width}")
             width = table_width
         num_groups = len(manager.groups)
-        if sampling is not None and len(sampling) != len(rows):
-            raise ValueError(f"{len(sampling)} sampling rows for {len(rows)} wanted places")
+        if sampling is not None and len(sampling) != len(rows) - pads:
+            raise ValueError(f"{len(sampling)} sampling rows for {len(rows) - pads} wanted places")
         sizes = [total, total, total, b + 1, b, b, b, len(rows)] + [b * width, total] * num_groups
         first_sampling = len(sizes)
         if sampling is not None:
@@ -230,22 +245,27 @@ class BatchBuilder:
         page_index = positions // page
         offset = positions - page_index * page
         for g in range(num_groups):
-            table = manager.table_rows(g, slots_of, width)
-            page_of_token = table[seq_index, page_index]
+            table = manager.table_rows(g, slots_of[:real], width)
+            page_of_token = table[seq_index[: total - pads], page_index[: total - pads]]
             if int(page_of_token.min()) < 0:
                 bad = int(np.argmax(page_of_token < 0))
                 raise ValueError(
                     f"request {entries[int(seq_index[bad])].key!r}: position {int(positions[bad])} has no page in group {g}"
                 )
-            host[starts[8 + 2 * g] : starts[8 + 2 * g] + b * width].reshape(b, width)[:] = table
-            put(9 + 2 * g, page_of_token * page + offset)
+            tables = host[starts[8 + 2 * g] : starts[8 + 2 * g] + b * width].reshape(b, width)
+            tables[:real] = table
+            tables[real:] = 0                        # a padding row reads page 0
+            token_slots = host[starts[9 + 2 * g] : starts[9 + 2 * g] + total]
+            token_slots[: total - pads] = page_of_token * page + offset[: total - pads]
+            token_slots[total - pads :] = -1         # and writes nothing
         if sampling is not None:
             f = first_sampling
-            host[starts[f] : starts[f] + len(rows)].view(np.float32)[:] = [r.temperature for r in sampling]
-            put(f + 1, [_signed32(r.seed) for r in sampling])
-            put(f + 2, [_signed32(r.seed >> 32) for r in sampling])
-            put(f + 3, [_signed32(r.request_key) for r in sampling])
-            put(f + 4, [_signed32(r.output_index) for r in sampling])
+            zeros = [0] * pads
+            host[starts[f] : starts[f] + len(rows)].view(np.float32)[:] = [r.temperature for r in sampling] + [0.0] * pads
+            put(f + 1, [_signed32(r.seed) for r in sampling] + zeros)
+            put(f + 2, [_signed32(r.seed >> 32) for r in sampling] + zeros)
+            put(f + 3, [_signed32(r.request_key) for r in sampling] + zeros)
+            put(f + 4, [_signed32(r.output_index) for r in sampling] + zeros)
         dev = self.staging.commit(turn, size, into)
         self.bytes_uploaded = 4 * size
         spans = list(zip(starts, sizes))

@@ -68,7 +68,7 @@ class ModelRunner:
         self.graph_replays = 0
         # The token last sampled for the request in each state slot; a step's token id of -1
         # reads it, so a sampled token can feed the next step without a trip to the host.
-        self.last_token = torch.zeros(self.manager.slots.num_slots, dtype=torch.int32, device=self.runtime.device)
+        self.last_token = torch.zeros(self.manager.slots.num_slots + 1, dtype=torch.int32, device=self.runtime.device)
 
     def begin_request(self, key: Hashable) -> bool:
         """Registers a request (state slot, empty block tables); False when no slot is free."""
@@ -104,26 +104,36 @@ class ModelRunner:
         width = 16
         while width * page < longest:
             width *= 2
-        return (len(entries), width, sampling is not None)
+        return (self.graph_batch(len(entries)), width, sampling is not None)
+
+    @staticmethod
+    def graph_batch(count: int) -> int:
+        """The batch size whose graph a decode step of `count` requests replays: itself up to 8,
+        then the next multiple of 2 up to 16, of 4 up to 32, of 8 beyond (padding rows fill the
+        rest), so that a batch that shrinks and grows by ones records a few graphs, not one per size."""
+        if count <= 8:
+            return count
+        step = 2 if count <= 16 else (4 if count <= 32 else 8)
+        return -(-count // step) * step
 
     @torch.inference_mode()
     def step(self, entries: Sequence[StepEntry], sampling: Sequence[Any] | None = None) -> StepOutput:
         key = self._graph_key(entries, sampling)
         slot = self.graphs.get(key) if key is not None else None
         if slot is not None and slot.graph is not None:
-            self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer)
+            self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer, pad_to=key[0])
             slot.graph.replay()
             self.model.forward_pass_count += 1
             self.graph_replays += 1
             ops = self.runtime.ops
             if hasattr(ops, "launches"):
                 ops.launches += slot.launches
-            logits, tokens = slot.logits, slot.tokens
+            logits, tokens = slot.logits[: len(entries)], None if slot.tokens is None else slot.tokens[: len(entries)]
             num_tokens = len(entries)
         elif key is not None and len(self.graphs) < self.MAX_GRAPHS:
             # First time for this shape: its launches are recorded (nothing runs), then the
             # recording is replayed, which is this step's real work.
-            ctx = self.builder.build(entries, sampling, table_width=key[1])
+            ctx = self.builder.build(entries, sampling, table_width=key[1], pad_to=key[0])
             slot = _DecodeGraph(ctx.buffer)
             self._capture(slot, ctx)
             self.graphs[key] = slot
@@ -132,7 +142,7 @@ class ModelRunner:
             ops = self.runtime.ops
             if hasattr(ops, "launches"):
                 ops.launches += slot.launches
-            logits, tokens = slot.logits, slot.tokens
+            logits, tokens = slot.logits[: len(entries)], None if slot.tokens is None else slot.tokens[: len(entries)]
             num_tokens = len(entries)
         else:
             ctx = self.builder.build(entries, sampling)

@@ -77,6 +77,37 @@ def test_graph_steps_equal_eager_steps(tmp_path_factory, dtype_name):
         assert torch.equal(logits_g[rid], logits_e[rid])
 
 
+@pytest.mark.parametrize("config_name", ["tiny_b", "tiny_d"])
+def test_padded_graph_steps_equal_eager_steps(tmp_path_factory, config_name):
+    """Eleven, ten and nine requests decode through the graph of twelve (then of ten): rows that
+    pad a step up to its graph's batch size change nothing for the real ones, whose tokens and
+    logits are the same bits as without graphs; the requests end at different steps, so the
+    batch shrinks through several graphs."""
+    from paged_attention_engine_b200 import LLM, Request
+    from paged_attention_engine_b200.engine.runner import ModelRunner
+
+    assert [ModelRunner.graph_batch(n) for n in (1, 8, 9, 11, 16, 17, 33, 64)] == [1, 8, 10, 12, 16, 20, 40, 64]
+    folder, raw, page = _folder(tmp_path_factory, config_name, "bfloat16")
+    lengths = (9, 16, 33, 5, 21, 2, 40, 12, 7, 30, 18)
+    prompts = {f"p{i}": tuple(helpers.random_tokens(raw["vocab_size"], n, 700 + n)) for i, n in enumerate(lengths)}
+
+    def run(use_graphs):
+        llm = LLM.from_pretrained(folder, dtype="bfloat16", num_blocks=128, block_size=page, record_logits=True,
+                                  use_graphs=use_graphs, max_num_seqs=16)
+        for i, (rid, prompt) in enumerate(prompts.items()):
+            llm.add_request(Request(rid, prompt, 6 + 2 * i, temperature=0.5 if i % 2 else 0.0, seed=3))
+        out = llm.run_to_completion()
+        sizes = sorted({key[0] for key in llm.runner.graphs})
+        return out, {rid: torch.stack(llm.scheduler.finished[rid].step_logits) for rid in prompts}, sizes
+
+    out_g, logits_g, sizes = run(True)
+    out_e, logits_e, none = run(False)
+    assert 12 in sizes and 10 in sizes and 11 not in sizes and 9 not in sizes and not none
+    assert out_g == out_e
+    for rid in prompts:
+        assert torch.equal(logits_g[rid], logits_e[rid]), rid
+
+
 @pytest.mark.parametrize("dtype_name", list(DTYPES))
 def test_long_decoding_and_first_tokens(tmp_path_factory, dtype_name):
     """A one-token prompt decoded far past several page edges and graph widths: the first
