@@ -82,8 +82,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 //
 // A few kernels do read before the wait. The rule they keep: only memory that was last written
 // before the kernel BEFORE this one was launched, which is the only memory certain to be
-// complete at that point whatever the stream did between the two launches. The products read
-// their weights (written when the model was loaded); decode attention reads the step's
+// complete at that point whatever the stream did between the two launches. The products and
+// the fused norm read their weights (written when the model was loaded); decode attention reads the step's
 // integers and the keys and values of earlier tokens (written in earlier steps, and by the
 // copy that opens the step, which many kernels follow before the first attention); the merge
 // follows the sliced kernel of the same call. Everything else before a wait is a prefetch hint.

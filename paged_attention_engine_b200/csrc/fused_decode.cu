@@ -104,30 +104,25 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float* v) {
 // start on 16 bytes): 16-byte loads of the partial sums, twelve splits in flight at a time. Sums
 // run in the order of the splits, as above, so the rounded value is the same bits; the sum of
 // squares adds four columns per thread first, which may differ from the scalar kernel in the
-// last bit of the norm. A thread asks for the norm's weight and the bias of its first four
-// columns together with the partial sums, and keeps the values of those columns in registers
-// from the sum to the scaling, so nothing is read after the sum of squares is known.
+// last bit of the norm. A thread reads the norm's weight and the bias of its first four
+// columns before anything else, and keeps the values of those columns in registers from the
+// sum to the scaling, so nothing is read after the sum of squares is known.
 template <typename T>
 __global__ void __launch_bounds__(512) splitk_rms_norm_x4_kernel(T* __restrict__ normed, T* __restrict__ value,
                                                                  const float* __restrict__ partial, int splits,
                                                                  const float* __restrict__ bias, const T* __restrict__ residual,
                                                                  const float* __restrict__ weight, int rows, int width, float eps) {
-  // Before the wait for the kernel before, only hints: the norm's weight is read once a step,
-  // so it comes from DRAM; asking the L2 for it now makes the read below a hit. (A read here
-  // would need the caller's word that the tensor was written before the kernel before this one
-  // was launched.)
+  // The norm's weight and the bias are the model's: written when it was loaded, like the
+  // products' weights, so they are read before the wait for the kernel before (the weight is
+  // read once a step and comes from DRAM, which takes longer than the sums from L2).
   dependent_launch_trigger();
   const int quads = width / 4;
-  if ((int)threadIdx.x < quads && (threadIdx.x & 7) == 0) {
-    prefetch_l2(weight + 4 * threadIdx.x);
-    if (bias != nullptr) prefetch_l2(bias + 4 * threadIdx.x);
-  }
-  dependent_launch_wait();
   float w_first[4] = {0.f, 0.f, 0.f, 0.f}, b_first[4] = {0.f, 0.f, 0.f, 0.f};
-  if ((int)threadIdx.x < quads) {               // asked for together with the sums below, used after them
+  if ((int)threadIdx.x < quads) {
     load4(weight + 4 * threadIdx.x, w_first);
     if (bias != nullptr) load4(bias + 4 * threadIdx.x, b_first);
   }
+  dependent_launch_wait();
   extern __shared__ float row_values[];
   __shared__ float reduce[32];
   const int row = blockIdx.x;
