@@ -39,13 +39,15 @@ using namespace pae;
 
 
 constexpr int TILE_KEYS = 16;            // keys per MMA step of the decode kernel: never straddles a page
-constexpr int DECODE_WARPS = 4;
+constexpr int DECODE_WARPS = 4;         // warps (slices) per block of the cluster form
 // The sliced decode kernel: warps (slices) per block, and tiles of 16 keys that a warp keeps in
 // flight. A tile takes about a microsecond to arrive and a slice is a handful of tiles, so a
-// slice's time is its number of tiles divided by the depth, in microseconds; two warps of
-// four stages use the shared memory of four warps of two.
+// slice's time is its number of tiles divided by the depth, in microseconds. Measured at the
+// 1.5B shape, context 4096 (decode step, ms at batch 1 / 8 / 64): two stages and four warps
+// 1.44 / 1.53 / 2.99; four stages and two warps 1.21 / 1.33 / 2.95; three stages 1.22 / 1.32 /
+// 2.89 (four blocks an SM); six stages 1.19 / 1.35 / 3.19.
 constexpr int SLICE_WARPS = 2;
-constexpr int SLICE_STAGES = 4;
+constexpr int SLICE_STAGES = 3;
 constexpr int PREFILL_BQ = 64;           // query tokens per block
 constexpr int PREFILL_BKEYS = 64;        // keys per iteration
 constexpr float LOG2E = 1.4426950408889634f;
