@@ -8,6 +8,11 @@ a change to any file of the package.
     over portions and steps, and belongs to one request only.
   * the schedule names a layer twice (shared weights, a cache per run), and lets an entry
     read the keys and values that an earlier entry wrote.
+  * `top1_experts` is a feed-forward with routing: router logits in float32, every token
+    goes to the one expert with the highest logit, an expert is a small SiLU-gated network.
+  * `stretched_rotary` is another position encoding: rotation angles of positions divided by a
+    factor, for a chosen part of the frequencies only (the rest are not rotated). The
+    package's attention part uses it through the same `table(ctx)` as its own.
 
 These are toys for the test, not models of anything.
 """
@@ -49,6 +54,62 @@ def _register_toys():
                 state[-1] = counts[-1]
                 at += count
             return out
+
+    from paged_attention_engine_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, TensorSpec
+
+    @FEED_FORWARDS.register("top1_experts")
+    class Top1Experts(Part):
+        """params: hidden_size, intermediate_size, experts. tensors: router.weight [E, H] and, per
+        expert e, experts.e.gate_up.weight [2 I, H] and experts.e.down.weight [H, I]."""
+
+        graph_safe = False      # the routing is read back to the host
+
+        @classmethod
+        def tensor_specs(cls, spec):
+            h, i, e = (int(spec.params[k]) for k in ("hidden_size", "intermediate_size", "experts"))
+            specs = [TensorSpec(spec.tensor_name("router.weight"), (e, h), "matrix")]
+            for x in range(e):
+                specs.append(TensorSpec(spec.tensor_name(f"experts.{x}.gate_up.weight"), (2 * i, h), "matrix"))
+                specs.append(TensorSpec(spec.tensor_name(f"experts.{x}.down.weight"), (h, i), "matrix"))
+            return specs
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.experts = int(spec.params["experts"])
+            self.router = tensors[spec.tensor_name("router.weight")]
+            self.gate_up = [tensors[spec.tensor_name(f"experts.{x}.gate_up.weight")] for x in range(self.experts)]
+            self.down = [tensors[spec.tensor_name(f"experts.{x}.down.weight")] for x in range(self.experts)]
+
+        def forward(self, ctx, x, residual):
+            ops = self.ops
+            x = ops.materialized(x)
+            logits = ops.materialized(ops.linear(x, self.router, out_dtype=torch.float32))     # float32 router logits
+            choice = logits.argmax(dim=-1)
+            out = residual.clone()
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    hidden = ops.silu_mul(ops.linear(x[rows].contiguous(), self.gate_up[e]))
+                    out[rows] += ops.materialized(ops.linear(hidden, self.down[e])).to(out.dtype)
+            return out
+
+    @POSITION_ENCODINGS.register("stretched_rotary")
+    class StretchedRotary(Part):
+        """params: head_dim, theta, factor, rotated (how many of the head_dim / 2 frequencies rotate)."""
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            d, theta = int(spec.params["head_dim"]), float(spec.params["theta"])
+            inv_freq = 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.int64).to(torch.float32) / d))
+            inv_freq = inv_freq / float(spec.params["factor"])
+            inv_freq[int(spec.params["rotated"]):] = 0.0          # angle 0: cosine 1, sine 0
+            self.inv_freq = inv_freq.to(runtime.device)
+            self._key = ("stretched_rotary", d, theta, float(spec.params["factor"]), int(spec.params["rotated"]))
+
+        def table(self, ctx):
+            if self._key not in ctx.memo:
+                ctx.memo[self._key] = self.ops.rotary_table(ctx.positions, self.inv_freq)
+            return ctx.memo[self._key]
 
 
 def _spec(hidden, vocab, schedule_kind):
@@ -145,3 +206,106 @@ def test_toy_model_is_registered_built_and_stepped(schedule_kind):
         gap = (got[key] - want).abs().max().item()
         assert gap <= helpers.tolerance(torch.float32, want), f"{schedule_kind}/{key}: {gap}"
     assert cache.manager.slots.num_free == 3 and cache.manager.allocators[0].num_free == 24
+
+
+def _routed_spec(hidden, vocab):
+    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    def norm(prefix):
+        return PartSpec("rms_norm", {"size": hidden, "eps": 1e-5}, prefix)
+
+    def attention(prefix):
+        return PartSpec("gqa_attention", {
+            "hidden_size": hidden, "num_heads": 4, "num_kv_heads": 1, "head_dim": 16, "qkv_bias": True, "scale": 0.25,
+            "window": 0, "position_encoding": {"kind": "stretched_rotary", "head_dim": 16, "theta": 1e4, "factor": 4.0, "rotated": 5}},
+            prefix)
+
+    layers = (
+        LayerSpec("pre_norm_residual", norm("l0.n1"), attention("l0.attn"), norm("l0.n2"),
+                  PartSpec("top1_experts", {"hidden_size": hidden, "intermediate_size": 24, "experts": 3}, "l0.ff")),
+        LayerSpec("pre_norm_residual", norm("l1.n1"), attention("l1.attn"), norm("l1.n2"),
+                  PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48}, "l1.ff")),
+    )
+    return ModelSpec("toy_routed", vocab, hidden, 256, PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden}, "emb"),
+                     layers, (ScheduleEntry(0), ScheduleEntry(1)), norm("final"),
+                     PartSpec("lm_head", {"vocab_size": vocab, "hidden_size": hidden, "tied_to": "emb.weight"}, "head"))
+
+
+def _plain_routed_forward(w, ids):
+    """The routed toy model, whole sequence, with the plain implementation's functions."""
+    from plain import qwen2_plain as plain
+
+    x = w["emb.weight"][torch.tensor(ids)]
+    n = len(ids)
+    inv_freq = plain.rotary_inv_freq(16, 1e4) / 4.0
+    inv_freq[5:] = 0.0
+    cos, sin = plain.rotary_tables(inv_freq, torch.arange(n), torch.float32)
+    for layer in (0, 1):
+        p = f"l{layer}."
+        normed = plain.rms_norm(x, w[p + "n1.weight"], 1e-5)
+        q = plain.apply_rotary(plain.linear(normed, w[p + "attn.q_proj.weight"], w[p + "attn.q_proj.bias"]).view(n, 4, 16), cos, sin)
+        k = plain.apply_rotary(plain.linear(normed, w[p + "attn.k_proj.weight"], w[p + "attn.k_proj.bias"]).view(n, 1, 16), cos, sin)
+        v = plain.linear(normed, w[p + "attn.v_proj.weight"], w[p + "attn.v_proj.bias"]).view(n, 1, 16)
+        x = x + plain.linear(plain.attention(q, k, v, 0.25).reshape(n, 64), w[p + "attn.o_proj.weight"])
+        normed = plain.rms_norm(x, w[p + "n2.weight"], 1e-5)
+        if layer == 0:
+            choice = plain.linear(normed, w[p + "ff.router.weight"]).argmax(dim=-1)
+            update = torch.zeros_like(x)
+            for e in range(3):
+                rows = choice == e
+                gate_up = plain.linear(normed[rows], w[p + f"ff.experts.{e}.gate_up.weight"])
+                inner = gate_up.shape[1] // 2
+                hidden = torch.nn.functional.silu(gate_up[:, :inner]) * gate_up[:, inner:]
+                update[rows] = plain.linear(hidden, w[p + f"ff.experts.{e}.down.weight"])
+            x = x + update
+        else:
+            x = x + plain.swiglu(normed, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, w["final.weight"], 1e-5), w["emb.weight"]), choice
+
+
+def test_routed_feed_forward_and_another_position_encoding():
+    """A feed-forward that routes tokens to experts and a position encoding that is not the
+    package's, both defined above, in a model that is built and stepped in portions and single
+    tokens like any other; compared with the same model written out whole."""
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.kernels import ops
+    from paged_attention_engine_b200.parts import Runtime
+    from paged_attention_engine_b200.weights import collect_tensor_specs, place_tensors
+    from paged_attention_engine_b200.weights.random_init import draw
+
+    _register_toys()
+    hidden, vocab = 64, 89
+    spec = _routed_spec(hidden, vocab)
+    gen = torch.Generator().manual_seed(19)
+    raw = {}
+    for name, t in sorted(collect_tensor_specs(spec).items()):
+        scale = 5.0 if ".q_proj." in name or ".k_proj." in name else (25.0 if "router" in name else 1.0)
+        raw[name] = draw(t, gen) * scale        # a sharp router: no token sits on the fence between two experts
+    runtime = Runtime(ops, torch.float32, torch.device("cuda:0"))
+    engine = Engine(None, spec, place_tensors(dict(raw), spec, torch.float32, runtime.device), runtime)
+    assert not engine.model.graph_safe, "the routing reads the step on the host: no graph is recorded"
+    cache = engine.new_paged_cache(num_blocks=24, block_size=8, max_num_seqs=3)
+    runner = engine.new_runner(cache)
+    requests = {"a": helpers.random_tokens(vocab, 37, 5), "b": helpers.random_tokens(vocab, 26, 6), "c": helpers.random_tokens(vocab, 19, 7)}
+    trace = helpers.trace_mixed(requests, seed=8, live_limit=2, decode_tail=5)
+    outputs = {}
+    for record in trace:
+        entries = []
+        for item in record["entries"]:
+            if not cache.manager.is_live(item["id"]):
+                assert runner.begin_request(item["id"])
+            assert cache.manager.reserve(item["id"], len(item["tokens"])).ok
+            entries.append(StepEntry(item["id"], item["tokens"], item["want"]))
+        outputs[record["step"]] = runner.step(entries).logits.float().cpu()
+        for key in record["end"]:
+            runner.end_request(key)
+    got = helpers.collect(trace, outputs, requests)
+    used = set()
+    for key, ids in requests.items():
+        want, choice = _plain_routed_forward(raw, ids)
+        used |= set(choice.tolist())
+        gap = (got[key] - want).abs().max().item()
+        assert gap <= helpers.tolerance(torch.float32, want), f"{key}: {gap}"
+    assert used == {0, 1, 2}, "every expert got tokens"
+    assert cache.manager.allocators[0].num_free == 24
