@@ -92,6 +92,18 @@ def plain_logits(folder: Path, token_ids) -> torch.Tensor:
     return plain.forward_logits(list(token_ids), weights, cfg)
 
 
+def teacher_forced_check(folder, dtype, prompt, tokens, step_logits):
+    """Greedy tokens may differ between precisions where two logits nearly tie; what must hold is
+    that every step's logits are those of the plain model for the engine's own token history."""
+    oracle = plain_logits(folder, list(prompt) + list(tokens))[len(prompt) - 1 : -1]
+    got = torch.stack(step_logits)
+    gap = (got - oracle).abs().max().item()
+    assert gap <= tolerance(dtype, oracle), f"max |dlogit| {gap}"
+    margin = 2 * tolerance(dtype, oracle)
+    for row, token in zip(oracle, tokens):
+        assert row[token].item() >= row.max().item() - margin, "the sampled token is not the plain model's best"
+
+
 def random_tokens(vocab: int, count: int, seed: int) -> list[int]:
     gen = torch.Generator().manual_seed(seed)
     return torch.randint(0, vocab, (count,), generator=gen).tolist()

@@ -19,16 +19,7 @@ def _folder(tmp_path_factory, name, dtype_name, sharpen=4.0):
     return folder, raw, page
 
 
-def _teacher_forced_check(folder, dtype, prompt, tokens, step_logits):
-    """Greedy tokens may differ between precisions where two logits nearly tie; what must hold is
-    that every step's logits are those of the plain model for the engine's own token history."""
-    oracle = helpers.plain_logits(folder, list(prompt) + list(tokens))[len(prompt) - 1 : -1]
-    got = torch.stack(step_logits)
-    gap = (got - oracle).abs().max().item()
-    assert gap <= helpers.tolerance(dtype, oracle), f"max |dlogit| {gap}"
-    margin = 2 * helpers.tolerance(dtype, oracle)
-    for row, token in zip(oracle, tokens):
-        assert row[token].item() >= row.max().item() - margin, "the sampled token is not the plain model's best"
+_teacher_forced_check = helpers.teacher_forced_check
 
 
 @pytest.mark.parametrize("name", list(helpers.TINY))

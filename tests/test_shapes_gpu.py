@@ -55,3 +55,30 @@ def test_drawn_configuration_agrees_with_the_plain_implementation(tmp_path, seed
         for key in requests:
             gap = (got[key] - wants[key]).abs().max().item()
             assert gap <= helpers.tolerance(dtype, wants[key]), f"seed {seed} {raw} page {page}: {key} off by {gap}"
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
+def test_drawn_configuration_generates_under_pressure(tmp_path, seed, dtype_name):
+    """Eleven requests at once through the entry point, with a pool too small for all of them
+    (requests are preempted and recomputed) and decode steps that replay padded graphs: every
+    step's logits are the plain model's for the engine's own token history."""
+    from paged_attention_engine_b200 import LLM, EventKind, Request
+
+    raw, page = _config(50 + seed)
+    dtype = torch.bfloat16 if dtype_name == "bfloat16" else torch.float32
+    folder = helpers.write_model(tmp_path / "model", raw, seed, dtype, sharpen=3.0)
+    rng = random.Random(200 + seed)
+    prompts = {f"q{i}": tuple(helpers.random_tokens(raw["vocab_size"], rng.randint(1, 45), 20 * seed + i)) for i in range(11)}
+    new_tokens = {rid: rng.randint(6, 20) for rid in prompts}
+    needs = [-(-(len(p) + new_tokens[rid]) // page) for rid, p in prompts.items()]
+    pool = max(max(needs) + 2, sum(needs) * 2 // 5)
+    llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=pool, block_size=page, max_num_seqs=12,
+                              max_num_batched_tokens=64, record_logits=True)
+    for rid, prompt in prompts.items():
+        assert llm.add_request(Request(rid, prompt, new_tokens[rid], temperature=0.0))
+    out = llm.run_to_completion()
+    for rid, prompt in prompts.items():
+        assert len(out[rid]) == new_tokens[rid]
+        helpers.teacher_forced_check(folder, dtype, prompt, out[rid], llm.scheduler.finished[rid].step_logits)
+    assert llm.cache.manager.allocators[0].num_free == pool, "every page came back"
