@@ -38,6 +38,7 @@ constexpr int BM = 128;          // MMA rows per tile
 constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
+constexpr int PERSISTENT_THREADS = 320;     // TMA warp, MMA warp, eight epilogue warps (two per quarter of the rows)
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 enum Mode : int { NORMAL = 0, SWAPPED = 1 };
@@ -482,7 +483,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 // output tiles. Four 48 KB stages keep about a microsecond of loads in flight; the
 // accumulator is double-buffered in tensor memory (2 x 256 columns), so the epilogue of a
 // tile (tcgen05.ld, bias, residual, rounding, stores) runs while the MMAs of the next tile
-// are issued. Tiles that share a weight tile are neighbours in the walk, so a weight tile
+// are issued. Eight warps run it, two for each quarter of the rows: with four the epilogue of
+// a tile (SiLU x up above all) took longer than the tile's MMAs and set the pace. Tiles that share a weight tile are neighbours in the walk, so a weight tile
 // is read from memory once and found in L2 by the other blocks.
 // ---------------------------------------------------------------------------------------
 template <int PBN>
@@ -500,7 +502,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 
 template <int PBN>
-__global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                           const __grid_constant__ CUtensorMap map_b,
                                                                           const Params p, int tiles_a, int tiles_b) {
   constexpr int PSTAGES = PTile<PBN>::STAGES;
@@ -532,7 +534,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 128);       // every epilogue thread arrives
+      mbar_init(tmem_empty_bar(a), PERSISTENT_THREADS - 64);       // every epilogue thread arrives
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -613,6 +615,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
     }
   } else {
     const int quadrant = warp & 3;
+    const bool second = warp >= 6;                  // warps 2-5 and 6-9: the two of each quarter
     const int row_in_tile = quadrant * 32 + lane;
     int local = 0;
     bool ok = true;
@@ -625,6 +628,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
       tcgen05_fence_after();
       const int row = tile_a * BM + row_in_tile;
       const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
+      // The two warps of a quarter of the rows share the tile's columns: the first takes
+      // [0, cut), the second [cut, PBN); the cut lies on a multiple of 32 columns (a gate block
+      // with its up block) or of the head size.
+      const int unit = p.rotary ? p.head_dim : 32;
+      const int cut = ((PBN / 2 + unit - 1) / unit) * unit;
+      const int col_begin = second ? min(cut, PBN) : 0, col_end = second ? PBN : min(cut, PBN);
       if (p.rotary) {
         // 16 columns of each half of a head at a time; the token's cosines and sines of those
         // 16 frequencies are read once and serve every head of the tile.
@@ -643,7 +652,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
             }
           }
 #pragma unroll 1
-          for (int head0 = 0; head0 < PBN; head0 += d) {
+          for (int head0 = col_begin; head0 < col_end; head0 += d) {
             float lo[16], hi[16];
             tmem_load16(lane_address + head0 + f0, lo);
             tmem_load16(lane_address + head0 + half + f0, hi);
@@ -653,7 +662,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
         }
       } else if (p.swiglu) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < PBN; c0 += 32) {
+        for (int c0 = col_begin; c0 < col_end; c0 += 32) {
           float gate[16], up[16];
           tmem_load16(lane_address + c0, gate);
           tmem_load16(lane_address + c0 + 16, up);
@@ -662,7 +671,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
         }
       } else {
 #pragma unroll 1
-        for (int c0 = 0; c0 < PBN; c0 += 16) {
+        for (int c0 = col_begin; c0 < col_end; c0 += 16) {
           float v[16];
           tmem_load16(lane_address + c0, v);
           const int col0 = tile_b * PBN + c0;
@@ -670,7 +679,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_persistent_kernel(const 
         }
       }
       tcgen05_fence_before();
-      mbar_arrive(tmem_empty_bar(acc));        // this thread has read its lane of the accumulator
+      mbar_arrive(tmem_empty_bar(acc));        // this thread has read its part of the accumulator
     }
   }
 
@@ -783,7 +792,7 @@ int launch_persistent_with(const Params& p, const void* a, const void* b, int k,
   }
   const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + PBN - 1) / PBN;
   const int blocks = tiles_a * tiles_b < sm_count() ? tiles_a * tiles_b : sm_count();
-  launch_kernel(gemm_tcgen05_persistent_kernel<PBN>, dim3(blocks), THREADS, T::SMEM_BYTES, stream, map_a, map_b, p, tiles_a, tiles_b);
+  launch_kernel(gemm_tcgen05_persistent_kernel<PBN>, dim3(blocks), PERSISTENT_THREADS, T::SMEM_BYTES, stream, map_a, map_b, p, tiles_a, tiles_b);
   return check_launch("linear_tcgen05");
 }
 
