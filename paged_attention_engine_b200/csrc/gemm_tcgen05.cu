@@ -38,7 +38,8 @@ constexpr int BM = 128;          // MMA rows per tile
 constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr int PERSISTENT_THREADS = 320;     // TMA warp, MMA warp, eight epilogue warps (two per quarter of the rows)
+constexpr int EPILOGUE_SHARES = 2;           // epilogue warps per quarter of the rows (three were measured slower, one much slower)
+constexpr int PERSISTENT_THREADS = 64 + 128 * EPILOGUE_SHARES;     // TMA warp, MMA warp, the epilogue warps
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 
 enum Mode : int { NORMAL = 0, SWAPPED = 1 };
@@ -615,7 +616,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
     }
   } else {
     const int quadrant = warp & 3;
-    const bool second = warp >= 6;                  // warps 2-5 and 6-9: the two of each quarter
+    const int share = (warp - 2) >> 2;              // which of the warps of this quarter
     const int row_in_tile = quadrant * 32 + lane;
     int local = 0;
     bool ok = true;
@@ -628,12 +629,11 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       tcgen05_fence_after();
       const int row = tile_a * BM + row_in_tile;
       const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
-      // The two warps of a quarter of the rows share the tile's columns: the first takes
-      // [0, cut), the second [cut, PBN); the cut lies on a multiple of 32 columns (a gate block
-      // with its up block) or of the head size.
+      // The warps of a quarter of the rows share the tile's columns in equal ranges that end
+      // on a multiple of 32 columns (a gate block with its up block) or of the head size.
       const int unit = p.rotary ? p.head_dim : 32;
-      const int cut = ((PBN / 2 + unit - 1) / unit) * unit;
-      const int col_begin = second ? min(cut, PBN) : 0, col_end = second ? PBN : min(cut, PBN);
+      const int range = ((PBN + EPILOGUE_SHARES - 1) / EPILOGUE_SHARES + unit - 1) / unit * unit;
+      const int col_begin = min(share * range, PBN), col_end = min(col_begin + range, PBN);
       if (p.rotary) {
         // 16 columns of each half of a head at a time; the token's cosines and sines of those
         // 16 frequencies are read once and serve every head of the tile.
