@@ -1,6 +1,6 @@
 // Attention of prompt portions over the paged cache on the fifth-generation tensor cores:
 // both products of attention are tcgen05.mma with accumulators in tensor memory, keys and
-// values come page by page through TMA, and the softmax runs with one thread per query row.
+// values come page by page through TMA, and the softmax runs in plain threads beside them.
 //
 // A block owns 128 consecutive query tokens of one request and one query head, and walks
 // that request's keys 128 at a time:
@@ -10,13 +10,16 @@
 //               stages deep. Pages are found through the block table; nothing is gathered.
 //   warp 1      MMA: S = Q . K^T into one of two score buffers in tensor memory (so the
 //               scores of the next tile are computed while the softmax works on this one),
-//               then O_tile = P . V once the probabilities are in shared memory. V is used
-//               as it lies in the cache (head dimension contiguous): an MN-major operand.
-//   warps 2-5   softmax: thread r owns query row r. It reads its row of scores from tensor
-//               memory twice (maximum; then exponentials, sum and the bfloat16
-//               probabilities written to shared memory in the operand's swizzled layout),
-//               then reads its row of O_tile and folds it into its running output in
-//               registers: out = out * 2^(old max - new max) + O_tile. No shuffles.
+//               then O_tile = P . V, into one of two product buffers, once the probabilities
+//               are in one of two buffers in shared memory. V is used as it lies in the
+//               cache (head dimension contiguous): an MN-major operand.
+//   warps 2-9   softmax: two threads share query row r (half of a tile's keys and half of
+//               the output's dimensions each). A thread reads its scores from tensor memory
+//               twice (maximum; then exponentials, sum and the bfloat16 probabilities
+//               written to shared memory in the operand's swizzled layout). The product of
+//               a tile is folded into the running output in registers one tile late,
+//               out = out * 2^(old max - new max) + O_tile, so the tensor core computes it
+//               while the threads take the next tile's exponentials. No shuffles.
 //
 // The rule of the reference (engine/attention.py:581-586) is evaluated per score on tiles
 // that touch the diagonal, a window's edge or the request's end; tiles that lie wholly
@@ -175,20 +178,22 @@ struct Layout {
   static constexpr int HALF_TILE_BYTES = 128 * 64 * 2;     // 128 rows x 64 bfloat16 = 16 KB
   static constexpr int Q_BYTES = HALVES * HALF_TILE_BYTES;
   static constexpr int KV_BYTES = HALVES * HALF_TILE_BYTES;   // one stage of K, or of V
-  static constexpr int P_BYTES = 2 * HALF_TILE_BYTES;         // 128 rows x 128 keys
+  static constexpr int P_BYTES = 2 * HALF_TILE_BYTES;         // 128 rows x 128 keys, one of two buffers
   static constexpr int Q_OFFSET = 0;
   static constexpr int K_OFFSET = Q_BYTES;                    // two stages
   static constexpr int V_OFFSET = K_OFFSET + 2 * KV_BYTES;
   static constexpr int P_OFFSET = V_OFFSET + 2 * KV_BYTES;
-  static constexpr int BAR_OFFSET = P_OFFSET + P_BYTES;
+  static constexpr int BAR_OFFSET = P_OFFSET + 2 * P_BYTES;
   static constexpr int EXCHANGE_OFFSET = BAR_OFFSET + 256;    // [2][128] floats that the two threads of a row swap
   static constexpr size_t SMEM_BYTES = (size_t)EXCHANGE_OFFSET + 1024 /* exchange */ + 1024 /* alignment */;
   static constexpr int S_COLUMNS = 128;                       // per score buffer
-  static constexpr int O_COLUMN = 2 * S_COLUMNS;              // O_tile behind the two score buffers
+  static constexpr int O_COLUMN = 2 * S_COLUMNS;              // two tiles' products behind the two score buffers
   static constexpr int TMEM_COLUMNS = 512;
+  static_assert(O_COLUMN + 2 * D <= TMEM_COLUMNS, "two score buffers and two products must fit tensor memory");
+  static_assert(SMEM_BYTES <= 227 * 1024, "the block's shared memory");
 };
 
-enum Bar : int { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_READY = 13, O_FULL = 14, O_EMPTY = 15, X_READY = 16, NUM_BARS = 17 };
+enum Bar : int { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_READY = 13, O_FULL = 15, O_EMPTY = 17, X_READY = 19, NUM_BARS = 20 };
 
 template <int D>
 __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -220,10 +225,10 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
       mbar_init(bar(V_EMPTY, i), 1);
       mbar_init(bar(S_FULL, i), 1);
       mbar_init(bar(S_EMPTY, i), SOFTMAX_THREADS);
+      mbar_init(bar(P_READY, i), SOFTMAX_THREADS);
+      mbar_init(bar(O_FULL, i), 1);
+      mbar_init(bar(O_EMPTY, i), SOFTMAX_THREADS);
     }
-    mbar_init(bar(P_READY), SOFTMAX_THREADS);
-    mbar_init(bar(O_FULL), 1);
-    mbar_init(bar(O_EMPTY), SOFTMAX_THREADS);
     mbar_init(bar(X_READY), SOFTMAX_THREADS);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -347,16 +352,16 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
         if (t + 1 < n_tiles) issue_scores(t + 1);
         const int st = t & 1;
         ok = ok && mbar_wait(bar(V_FULL, st), (t >> 1) & 1, abort_flag, p.error, 5);
-        ok = ok && mbar_wait(bar(P_READY), t & 1, abort_flag, p.error, 6);
-        if (t >= 1) ok = ok && mbar_wait(bar(O_EMPTY), (t - 1) & 1, abort_flag, p.error, 7);
+        ok = ok && mbar_wait(bar(P_READY, st), (t >> 1) & 1, abort_flag, p.error, 6);
+        if (t >= 2) ok = ok && mbar_wait(bar(O_EMPTY, st), ((t >> 1) - 1) & 1, abort_flag, p.error, 7);
         if (!ok) break;
         tcgen05_fence_after();
-        const uint32_t p_addr = base + L::P_OFFSET, v_addr = base + L::V_OFFSET + st * L::KV_BYTES;
+        const uint32_t p_addr = base + L::P_OFFSET + st * L::P_BYTES, v_addr = base + L::V_OFFSET + st * L::KV_BYTES;
 #pragma unroll
         for (int k = 0; k < BKEYS / 16; ++k)     // 16 keys a step: two groups of 8 rows of V
-          umma_bf16(tmem_base + L::O_COLUMN, k_major_descriptor(p_addr + (k >> 2) * L::HALF_TILE_BYTES + (k & 3) * 32),
+          umma_bf16(tmem_base + L::O_COLUMN + st * D, k_major_descriptor(p_addr + (k >> 2) * L::HALF_TILE_BYTES + (k & 3) * 32),
                     mn_major_descriptor(v_addr + k * 2048, L::HALF_TILE_BYTES), idesc_o, k > 0 ? 1u : 0u);
-        tcgen05_commit(bar(O_FULL));
+        tcgen05_commit(bar(O_FULL, st));
         tcgen05_commit(bar(V_EMPTY, st));
       }
     }
@@ -366,6 +371,12 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
     // its 32 rows: one takes keys 0-63 of a tile and the first half of the output's
     // dimensions, the other keys 64-127 and the second half. They swap their maxima through
     // shared memory once per tile and their sums once at the end.
+    //
+    // P and a tile's product P.V have two buffers each, and a tile's product is added to the
+    // output one tile late: after the probabilities of tile t are handed over, the threads add
+    // the product of tile t-1, which the tensor core finished while they were taking
+    // exponentials. So the product of one tile runs under the softmax of the next, and the
+    // threads wait for neither.
     const int quadrant = warp & 3;
     const int side = (warp - 2) >> 2;                         // which half of the keys and of the dimensions
     const int r = quadrant * 32 + lane;                       // row of the tile, lane of tensor memory
@@ -379,6 +390,24 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
     for (int i = 0; i < HALF_D; ++i) acc[i] = 0.f;
     float row_max = -FLT_MAX, row_sum = 0.f;
     bool ok = true;
+    // acc = acc * scale + the product of tile u (scale: what tile u's maximum did to the reference).
+    auto add_product = [&](int u, float scale) {
+      const int su = u & 1;
+      ok = ok && mbar_wait(bar(O_FULL, su), (u >> 1) & 1, abort_flag, p.error, 9);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      tcgen05_fence_after();
+#pragma unroll
+      for (int c = 0; c < HALF_D; c += 32) {
+        float o[32];
+        tmem_load32(lane_base + L::O_COLUMN + su * D + side * HALF_D + c, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * scale + o[i];
+      }
+      tcgen05_fence_before();
+      mbar_arrive(bar(O_EMPTY, su));
+    };
+    float owed_scale = 0.f;       // goes with the product that is not added yet
     for (int t = 0; t < n_tiles; ++t) {
       const int st = t & 1;
       const int key0 = kv_begin + t * BKEYS;
@@ -424,7 +453,7 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
       const float offset = new_max == -FLT_MAX ? 0.f : -new_max;
       const float factor = new_max == -FLT_MAX ? 0.f : p.scale_log2;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* p_row = generic_base + L::P_OFFSET + r * 128;
+      uint8_t* p_row = generic_base + L::P_OFFSET + st * L::P_BYTES + r * 128;
 #pragma unroll
       for (int c = side * HALF_KEYS; c < side * HALF_KEYS + HALF_KEYS; c += 32) {
         float s[32];
@@ -459,21 +488,12 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
       tcgen05_fence_before();
       mbar_arrive(bar(S_EMPTY, st));                            // this thread's part of the score buffer is read
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is for the tensor core's eyes
-      mbar_arrive(bar(P_READY));
-      ok = mbar_wait(bar(O_FULL), t & 1, abort_flag, p.error, 9);
-      ok = __all_sync(0xffffffffu, ok);
+      mbar_arrive(bar(P_READY, st));
+      if (t >= 1) add_product(t - 1, owed_scale);
       if (!ok) break;
-      tcgen05_fence_after();
-#pragma unroll
-      for (int c = 0; c < HALF_D; c += 32) {
-        float o[32];
-        tmem_load32(lane_base + L::O_COLUMN + side * HALF_D + c, o);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c + i] = acc[c + i] * rescale + o[i];
-      }
-      tcgen05_fence_before();
-      mbar_arrive(bar(O_EMPTY));
+      owed_scale = rescale;
     }
+    if (n_tiles > 0 && ok) add_product(n_tiles - 1, owed_scale);
     // The row's sum is the two threads' sums (both are relative to the same maximum).
     ok = __all_sync(0xffffffffu, ok);
     if (active && ok) {
