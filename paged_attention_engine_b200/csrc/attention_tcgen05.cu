@@ -26,6 +26,12 @@
 // inside need no mask. Scores are scaled in float32; probabilities are rounded to bfloat16
 // for the second product. Every mbarrier wait is bounded and reports through `error`.
 //
+// When a launch has few blocks (a short portion of a prompt over a long context), a query
+// tile's keys are shared out over a thread-block cluster: every block of the cluster takes a
+// run of key tiles, the blocks behind the first leave their rows' maxima, sums and outputs in
+// their own shared memory, and the first merges them through distributed shared memory
+// between two barriers of the cluster.
+//
 // Sizes: head_dim 64 or 128; page sizes 16, 32, 64 or 128; any number of heads and groups.
 // Requests that bring a single token are left to the decode kernel.
 #include <cuda.h>
@@ -138,6 +144,27 @@ __device__ __forceinline__ void tmem_load32(uint32_t address, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The cluster's barrier (every thread of every block of the cluster arrives and waits), this
+// block's place in its cluster, and a float read from the shared memory of another block of it.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+  return n;
+}
+__device__ __forceinline__ float load_from_block(uint32_t address, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(address), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -195,7 +222,7 @@ struct Layout {
 
 enum Bar : int { Q_FULL = 0, K_FULL = 1, V_FULL = 3, K_EMPTY = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11, P_READY = 13, O_FULL = 15, O_EMPTY = 17, X_READY = 19, NUM_BARS = 20 };
 
-template <int D>
+template <int D, bool SPLIT>
 __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                   const __grid_constant__ CUtensorMap map_k,
                                                                   const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -244,7 +271,10 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   dependent_launch_wait();
 
   // ---- what this block works on (the same in every role) -------------------------------
-  const int h = blockIdx.x, b = blockIdx.z;
+  // A cluster of `ranks` blocks shares one query tile of one head: each takes a run of its key
+  // tiles, and the first block folds the others' outputs into its own at the end.
+  const int ranks = SPLIT ? (int)cluster_size() : 1, rank = SPLIT ? (int)cluster_rank() : 0;
+  const int h = blockIdx.x / ranks, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   const int q_tiles = (q_count + BQ - 1) / BQ;
@@ -257,16 +287,29 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   const int pos0 = p.q_pos0[b] + tile * BQ;
   const int kv_end = active ? min(p.kv_len[b], pos0 + rows) : 0;
   const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int kv_begin = (first_key / p.page_size) * p.page_size;
-  const int n_tiles = active ? (kv_end - kv_begin + BKEYS - 1) / BKEYS : 0;
+  const int all_tiles = active ? (kv_end - (first_key / p.page_size) * p.page_size + BKEYS - 1) / BKEYS : 0;
+  const int tiles_per_rank = (all_tiles + ranks - 1) / ranks;
+  const int first_tile = min(rank * tiles_per_rank, all_tiles);
+  const int n_tiles = min(tiles_per_rank, all_tiles - first_tile);          // this block's
+  const int kv_begin = (first_key / p.page_size) * p.page_size + first_tile * BKEYS;
+  const bool working = n_tiles > 0;
   const int g = h / (p.heads / p.kv_heads);
+
+  // What the softmax threads carry out of their loop (the other warps leave it alone).
+  constexpr int HALF_D = D / 2;
+  const int quadrant = warp & 3;
+  const int side = warp >= 2 ? (warp - 2) >> 2 : 0;         // which half of the keys and of the dimensions
+  const int r = quadrant * 32 + lane;                       // row of the tile, lane of tensor memory
+  float acc[HALF_D];
+  float row_max = -FLT_MAX, row_sum = 0.f;
+  bool ok = true;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     // Lane i brings page i of a tile (its block-table entry and its boxes), so the table
     // look-ups of a tile are one round trip, not one per page. Lane 0 posts the byte counts
     // before any lane issues a copy.
-    if (active) {
+    if (working) {
       if (lane == 0) {
         mbar_expect_tx(bar(Q_FULL), L::Q_BYTES);
 #pragma unroll
@@ -327,7 +370,7 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && active) {
+    if (lane == 0 && working) {
       constexpr uint32_t idesc_s = instruction_descriptor(BQ, BKEYS, false);
       constexpr uint32_t idesc_o = instruction_descriptor(BQ, D, true);
       bool ok = mbar_wait(bar(Q_FULL), 0, abort_flag, p.error, 2);
@@ -377,19 +420,12 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
     // the product of tile t-1, which the tensor core finished while they were taking
     // exponentials. So the product of one tile runs under the softmax of the next, and the
     // threads wait for neither.
-    const int quadrant = warp & 3;
-    const int side = (warp - 2) >> 2;                         // which half of the keys and of the dimensions
-    const int r = quadrant * 32 + lane;                       // row of the tile, lane of tensor memory
     const uint32_t lane_base = tmem_base + ((uint32_t)(quadrant * 32) << 16);
     const int my_pos = pos0 + r;
     float* exchange = (float*)(generic_base + L::EXCHANGE_OFFSET);
-    constexpr int HALF_D = D / 2;
     constexpr int HALF_KEYS = BKEYS / 2;
-    float acc[HALF_D];
 #pragma unroll
     for (int i = 0; i < HALF_D; ++i) acc[i] = 0.f;
-    float row_max = -FLT_MAX, row_sum = 0.f;
-    bool ok = true;
     // acc = acc * scale + the product of tile u (scale: what tile u's maximum did to the reference).
     auto add_product = [&](int u, float scale) {
       const int su = u & 1;
@@ -496,24 +532,65 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
     if (n_tiles > 0 && ok) add_product(n_tiles - 1, owed_scale);
     // The row's sum is the two threads' sums (both are relative to the same maximum).
     ok = __all_sync(0xffffffffu, ok);
-    if (active && ok) {
+    if (working && ok) {
       exchange[side * 128 + r] = row_sum;
       mbar_arrive(bar(X_READY));
       ok = mbar_wait(bar(X_READY), n_tiles & 1, abort_flag, p.error, 12);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) row_sum += exchange[(side ^ 1) * 128 + r];
     }
-    if (ok && r < rows) {
-      const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
-      __nv_bfloat16* out = p.out + ((size_t)(first_token + tile * BQ + r) * p.heads + h) * D + side * HALF_D;
-#pragma unroll
-      for (int c = 0; c < HALF_D; c += 8) {
-        uint4 packed;
-        __nv_bfloat162* h2 = (__nv_bfloat162*)&packed;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(acc[c + 2 * e] * inv, acc[c + 2 * e + 1] * inv);
-        *(uint4*)(out + c) = packed;
+  }
+
+  if constexpr (SPLIT) {
+    // The blocks behind the first leave their rows' maxima, sums and outputs in their own
+    // shared memory, where the keys and values lay (every product that read those has
+    // completed: the softmax threads waited for the last one); the first block reads them
+    // there once the whole cluster has arrived, and nobody leaves before it has.
+    float* stage = (float*)(generic_base + L::K_OFFSET);              // [D][128]: a dimension's 128 rows side by side
+    float* stage_stats = (float*)(generic_base + L::V_OFFSET);        // [2][128]: maximum, sum
+    if (warp >= 2 && rank != 0) {
+      const bool has = working && ok;
+      if (side == 0) {
+        stage_stats[r] = has ? row_max : -FLT_MAX;
+        stage_stats[128 + r] = has ? row_sum : 0.f;
       }
+      if (has) {
+#pragma unroll
+        for (int i = 0; i < HALF_D; ++i) stage[(side * HALF_D + i) * 128 + r] = acc[i];
+      }
+    }
+    cluster_arrive();
+    cluster_wait();
+    if (warp >= 2 && rank == 0 && working && ok) {
+      for (int other = 1; other < ranks; ++other) {
+        const float their_sum = load_from_block(smem_u32(stage_stats + 128 + r), other);
+        if (their_sum > 0.f) {
+          const float their_max = load_from_block(smem_u32(stage_stats + r), other);
+          const float both = fmaxf(row_max, their_max);
+          const float mine = row_max == -FLT_MAX ? 0.f : fast_exp2(row_max - both);
+          const float theirs = fast_exp2(their_max - both);
+#pragma unroll
+          for (int i = 0; i < HALF_D; ++i)
+            acc[i] = acc[i] * mine + load_from_block(smem_u32(stage + (side * HALF_D + i) * 128 + r), other) * theirs;
+          row_sum = row_sum * mine + their_sum * theirs;
+          row_max = both;
+        }
+      }
+    }
+    cluster_arrive();
+    cluster_wait();
+  }
+
+  if (warp >= 2 && rank == 0 && ok && r < rows) {
+    const float inv = row_sum > 0.f ? 1.f / row_sum : 0.f;
+    __nv_bfloat16* out = p.out + ((size_t)(first_token + tile * BQ + r) * p.heads + h) * D + side * HALF_D;
+#pragma unroll
+    for (int c = 0; c < HALF_D; c += 8) {
+      uint4 packed;
+      __nv_bfloat162* h2 = (__nv_bfloat162*)&packed;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(acc[c + 2 * e] * inv, acc[c + 2 * e + 1] * inv);
+      *(uint4*)(out + c) = packed;
     }
   }
 
@@ -948,13 +1025,26 @@ int sm_count() {
   return count;
 }
 
-// form 0: the paired kernel when the launch has at least two blocks per SM, else the wide one;
-// 1: wide; 2: paired.
+// form 0 picks by the size of the launch: the paired kernel when it has at least two blocks per
+// SM; else the wide one, and when its blocks are fewer than half of the SMs (a short portion
+// of a prompt over a long context) a query tile's keys are shared out over a cluster of 2, 4 or
+// 8 blocks, as long as all blocks still run at once and each has two key tiles or more. A block
+// costs about 10 us around its tiles and only one fits an SM, so a second wave of blocks would
+// cost more than the shorter chains save: 128 tokens after 8,192 take 123 us in 12 blocks.
+// 1: wide, no clusters; 2: paired; 4, 8, 16: wide in clusters of 2, 4, 8.
 template <int D>
 int launch(const Params& p, const void* qkv, const void* keys, const void* values, int tokens, long long pages, int seqs,
-           int max_q_len, int form, cudaStream_t stream) {
+           int max_q_len, int max_kv_len, int form, cudaStream_t stream) {
   dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
-  const bool use_paired = form == 2 || (form == 0 && (long long)grid.x * grid.y * grid.z >= 2LL * sm_count());
+  const long long blocks = (long long)grid.x * grid.y * grid.z;
+  const bool use_paired = form == 2 || (form == 0 && blocks >= 2LL * sm_count());
+  unsigned ranks = 1;
+  if (form == 4 || form == 8 || form == 16) ranks = form / 2;
+  if (form == 0 && !use_paired) {
+    const int seen = p.window > 0 && p.window + BQ < max_kv_len ? p.window + BQ : max_kv_len;
+    const int longest = (seen + BKEYS - 1) / BKEYS;        // key tiles of the longest block
+    while (ranks < 8 && blocks * (ranks * 2) <= sm_count() && longest >= (int)(ranks * 2) * 2) ranks *= 2;
+  }
   CUtensorMap map_q, map_k, map_v;
   if (int err = tensor_map(&map_q, qkv, tokens, (p.heads + 2 * p.kv_heads) * D, BQ)) return err;
   const long long cache_rows = pages * p.kv_heads * p.page_size;
@@ -964,18 +1054,25 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
   if (int err = tensor_map(&map_v, values, cache_rows, D, box_rows)) return err;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<D>::SMEM_BYTES);
+    cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<D>::SMEM_BYTES);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(prefill_tcgen05_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Layout<D>::SMEM_BYTES);
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(paired::prefill_tcgen05_paired_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)paired::Layout<D>::SMEM_BYTES);
     if (err != cudaSuccess) return fail(100, "paged_attention_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
-  if (use_paired)
+  if (use_paired) {
     launch_kernel(paired::prefill_tcgen05_paired_kernel<D>, grid, paired::THREADS, paired::Layout<D>::SMEM_BYTES, stream, map_q, map_k,
                   map_v, p);
-  else
-    launch_kernel(prefill_tcgen05_kernel<D>, grid, THREADS, Layout<D>::SMEM_BYTES, stream, map_q, map_k, map_v, p);
+  } else {
+    grid.x *= ranks;
+    if (ranks > 1)
+      launch_kernel_cluster(prefill_tcgen05_kernel<D, true>, grid, dim3(THREADS), Layout<D>::SMEM_BYTES, stream, ranks, map_q, map_k, map_v, p);
+    else
+      launch_kernel(prefill_tcgen05_kernel<D, false>, grid, THREADS, Layout<D>::SMEM_BYTES, stream, map_q, map_k, map_v, p);
+  }
   return check_launch("paged_attention_tcgen05");
 }
 
@@ -991,8 +1088,8 @@ PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, in
 PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, const void* keys, const void* values,
                                                    long long pages, const int* block_table, int table_width,
                                                    const int* q_start, const int* q_pos0, const int* kv_len, int tokens,
-                                                   int seqs, int max_q_len, int heads, int kv_heads, int d, int page_size,
-                                                   float scale, int window, int skip_single, int form, int* error,
+                                                   int seqs, int max_q_len, int max_kv_len, int heads, int kv_heads, int d,
+                                                   int page_size, float scale, int window, int skip_single, int form, int* error,
                                                    void* stream) {
   if (seqs == 0 || max_q_len == 0 || tokens == 0) return 0;
   if (!pae_attention_tcgen05_supports(heads, kv_heads, d, page_size))
@@ -1015,8 +1112,8 @@ PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, c
   p.scale_log2 = scale * LOG2E;
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
-  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, form, s);
-  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, form, s);
+  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, max_kv_len, form, s);
+  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, max_kv_len, form, s);
 }
 
 PAE_DEFINE_LAST_ERROR()

@@ -208,6 +208,31 @@ def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True, 
     return tensors, kv_lens
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [(4, 2, 128, 16, 0), (6, 1, 64, 64, 0), (2, 2, 128, 32, 700)])
+@pytest.mark.parametrize("late_spike", [False, True])
+def test_short_portions_over_long_contexts_share_their_keys_over_a_cluster(ops, heads, kv_heads, d, page, window, late_spike):
+    """A few query tiles over thousands of keys: the launch is small enough that each query
+    tile's keys are shared out over a cluster of blocks by itself. One far key (the request's
+    key 3, in the first block's share) scores high for every query, with `late_spike` another
+    near the end (the last block's share) far higher, so a share that is dropped, or merged with
+    the wrong weight, shows."""
+    gen = torch.Generator().manual_seed(37)
+    q_lens, pos0 = [130, 64], [3000, 1900]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16, late_spike=late_spike)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
+    want = ref.paged_attention(*tensors, **args)
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    ops.check_device_errors()
+    _close(got, want, torch.bfloat16, scale=2.0)
+    ops.tcgen05_attention_form = 1
+    try:
+        alone = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    finally:
+        ops.tcgen05_attention_form = 0
+    assert (got.float() - alone.float()).abs().max().item() <= 2.0 ** -6 * float(alone.float().abs().max())
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [
     (12, 2, 128, 16, 0), (16, 1, 64, 32, 0), (3, 1, 32, 16, 0), (28, 4, 128, 16, 300), (8, 8, 64, 48, 0), (6, 2, 128, 64, 33),
 ])
@@ -270,12 +295,15 @@ def test_tensor_core_attention_agrees_with_the_cuda_core_kernel(ops):
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [
     (12, 2, 128, 16, 0), (4, 4, 64, 16, 0), (3, 1, 128, 32, 0), (6, 3, 128, 16, 100), (2, 1, 64, 64, 17), (5, 5, 128, 128, 0),
 ])
-@pytest.mark.parametrize("form,late_spike", [(1, False), (2, False), (1, True), (2, True)])
+@pytest.mark.parametrize("form,late_spike", [(1, False), (2, False), (1, True), (2, True), (4, False), (4, True), (8, True),
+                                             (16, False), (0, True)])
 def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window, form, late_spike):
     """The tcgen05 kernels (form 1: 128-key tiles, one block per SM; form 2: 64-key tiles, the
-    output kept in tensor memory, two blocks per SM): portions of 64 tokens and more at offsets
-    that are ragged against the 128-row tiles, the pages and the key tiles, beside shorter
-    portions and single tokens."""
+    output kept in tensor memory, two blocks per SM; forms 4, 8, 16: the first with a query
+    tile's keys shared out over a cluster of 2, 4, 8 blocks, whose outputs the first block
+    merges, some of them with no keys at all; 0: whichever the launch's size picks): portions of
+    64 tokens and more at offsets that are ragged against the 128-row tiles, the pages and the
+    key tiles, beside shorter portions and single tokens."""
     gen = torch.Generator().manual_seed(31)
     q_lens = [300, 1, 129, 2, 128, 1, 65, 700]
     pos0 = [0, 500, 1000, 31, 64, 0, 77, 5]
