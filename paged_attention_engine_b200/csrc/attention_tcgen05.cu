@@ -1034,9 +1034,10 @@ int sm_count() {
 // 1: wide, no clusters; 2: paired; 4, 8, 16: wide in clusters of 2, 4, 8.
 template <int D>
 int launch(const Params& p, const void* qkv, const void* keys, const void* values, int tokens, long long pages, int seqs,
-           int max_q_len, int max_kv_len, int form, cudaStream_t stream) {
+           int working_seqs, int max_q_len, int max_kv_len, int form, cudaStream_t stream) {
   dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
-  const long long blocks = (long long)grid.x * grid.y * grid.z;
+  // Blocks of requests that this launch leaves to the decode kernel return at once: they do not count.
+  const long long blocks = (long long)grid.x * grid.y * working_seqs;
   const bool use_paired = form == 2 || (form == 0 && blocks >= 2LL * sm_count());
   unsigned ranks = 1;
   if (form == 4 || form == 8 || form == 16) ranks = form / 2;
@@ -1084,12 +1085,12 @@ PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, in
 }
 
 // Attention of every request that brings more than one token (or every request, unless
-// skip_single). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests). qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
+// skip_single; `singles` is how many bring one, -1 when the caller does not know). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests). qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
 PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, const void* keys, const void* values,
                                                    long long pages, const int* block_table, int table_width,
                                                    const int* q_start, const int* q_pos0, const int* kv_len, int tokens,
                                                    int seqs, int max_q_len, int max_kv_len, int heads, int kv_heads, int d,
-                                                   int page_size, float scale, int window, int skip_single, int form, int* error,
+                                                   int page_size, float scale, int window, int skip_single, int singles, int form, int* error,
                                                    void* stream) {
   if (seqs == 0 || max_q_len == 0 || tokens == 0) return 0;
   if (!pae_attention_tcgen05_supports(heads, kv_heads, d, page_size))
@@ -1112,8 +1113,9 @@ PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, c
   p.scale_log2 = scale * LOG2E;
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
-  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, max_kv_len, form, s);
-  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, max_q_len, max_kv_len, form, s);
+  const int working_seqs = skip_single && singles > 0 && singles < seqs ? seqs - singles : seqs;
+  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, s);
+  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, s);
 }
 
 PAE_DEFINE_LAST_ERROR()

@@ -464,7 +464,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), ctypes.c_longlong(keys.shape[0]), _ptr(block_table),
                     c_int(block_table.shape[1]), _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(tokens), c_int(seqs),
                     c_int(max_q_len), c_int(max_kv_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
-                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), c_int(tcgen05_attention_form),
+                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), c_int(singles), c_int(tcgen05_attention_form),
                     _ptr(_error_flag(qkv.device)), _stream()))
                 if decode_after:
                     _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles,
