@@ -1025,6 +1025,8 @@ int sm_count() {
   return count;
 }
 
+int last_cluster_blocks = 0;     // of the last launch: 0 for the paired kernel, else blocks per query tile
+
 // form 0 picks by the size of the launch: the paired kernel when it has at least two blocks per
 // SM; else the wide one, and when its blocks are fewer than half of the SMs (a short portion
 // of a prompt over a long context) a query tile's keys are shared out over a cluster of 2, 4 or
@@ -1064,6 +1066,7 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
     if (err != cudaSuccess) return fail(100, "paged_attention_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
+  last_cluster_blocks = use_paired ? 0 : (int)ranks;
   if (use_paired) {
     launch_kernel(paired::prefill_tcgen05_paired_kernel<D>, grid, paired::THREADS, paired::Layout<D>::SMEM_BYTES, stream, map_q, map_k,
                   map_v, p);
@@ -1078,6 +1081,9 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
 }
 
 }  // namespace
+
+// Blocks per query tile in the last launch (1: no clusters; 0: the paired kernel). For tests.
+PAE_EXPORT int pae_attention_tcgen05_last_cluster() { return last_cluster_blocks; }
 
 PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, int page_size) {
   return (d == 64 || d == 128) && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128) &&

@@ -224,12 +224,14 @@ def test_short_portions_over_long_contexts_share_their_keys_over_a_cluster(ops, 
     want = ref.paged_attention(*tensors, **args)
     got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
     ops.check_device_errors()
+    assert ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster() >= (2 if window else 4)
     _close(got, want, torch.bfloat16, scale=2.0)
     ops.tcgen05_attention_form = 1
     try:
         alone = ops.paged_attention(*[t.cuda() for t in tensors], **args)
     finally:
         ops.tcgen05_attention_form = 0
+    assert ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster() == 1
     assert (got.float() - alone.float()).abs().max().item() <= 2.0 ** -6 * float(alone.float().abs().max())
 
 

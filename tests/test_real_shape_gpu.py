@@ -80,3 +80,58 @@ def test_portions_and_decoding_at_the_real_layer_sizes(folder, oracle, dtype_nam
         assert have.shape == want.shape
         gap = (have - want).abs().max().item()
         assert gap <= helpers.tolerance(dtype, want), f"{dtype_name}/{key}: max |dlogit| {gap:.3e} vs {helpers.tolerance(dtype, want):.3e}"
+
+
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
+def test_short_portions_after_a_long_one_at_the_real_layer_sizes(folder, dtype_name):
+    """A prompt of 1,800 tokens whose first 1,280 come in one step and the rest in portions of
+    192, 100 (beside another request's decoded tokens) and 228: the later portions are few query
+    tiles over many keys, which the bfloat16 attention shares out over clusters of blocks."""
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.engine.replay import Replayer
+    from paged_attention_engine_b200.kernels import ops
+
+    dtype = torch.bfloat16 if dtype_name == "bfloat16" else torch.float32
+    cfg = plain.read_config(folder)
+    weights = {k: v.float().cuda() for k, v in plain.read_weights(folder).items()}
+    ids = {"far": helpers.random_tokens(SHAPE["vocab_size"], 1800, 5), "near": helpers.random_tokens(SHAPE["vocab_size"], 90, 6)}
+    rows = {"far": [1279, 1300, 1471, 1472, 1571, 1572, 1700, 1799], "near": [79, 80, 81, 82, 89]}
+    want = {}
+    for key in ids:
+        hidden = plain.forward_hidden(torch.tensor(ids[key], device="cuda"), weights, cfg)
+        want[key] = plain.linear(hidden[rows[key]], plain.lm_head_weight(weights)).float().cpu()
+    del weights, hidden
+    torch.cuda.empty_cache()
+
+    engine = Engine.from_pretrained(folder, dtype_name)
+    replayer = Replayer(engine, max_tokens=2048, block_size=16)
+
+    def entry(key, start, count):
+        return {"id": key, "tokens": ids[key][start : start + count], "want": [r - start for r in rows[key] if start <= r < start + count]}
+
+    steps = [
+        [entry("far", 0, 1280), entry("near", 0, 80)],
+        [entry("far", 1280, 192), entry("near", 80, 1)],
+        [entry("far", 1472, 100), entry("near", 81, 1)],
+        [entry("far", 1572, 228), entry("near", 82, 8)],
+    ]
+    got = {key: [] for key in ids}
+    clusters = []
+    for i, entries in enumerate(steps):
+        out = replayer.run({"step": i, "entries": entries, "end": ["far", "near"] if i == len(steps) - 1 else []})
+        ops.check_device_errors()
+        if dtype_name == "bfloat16":
+            clusters.append(ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster())
+        at = 0
+        for e in entries:
+            n = len(e["want"])
+            if n:
+                got[e["id"]].append(out[at : at + n].float().cpu())
+                at += n
+    if dtype_name == "bfloat16":
+        assert clusters[0] == 1 and min(clusters[1:]) >= 2, clusters
+    for key in ids:
+        have = torch.cat(got[key])
+        assert have.shape == want[key].shape
+        gap = (have - want[key]).abs().max().item()
+        assert gap <= helpers.tolerance(dtype, want[key]), f"{dtype_name}/{key}: max |dlogit| {gap:.3e} vs {helpers.tolerance(dtype, want[key]):.3e}"
