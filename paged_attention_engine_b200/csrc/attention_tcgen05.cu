@@ -268,9 +268,11 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  dependent_launch_wait();
 
   // ---- what this block works on (the same in every role) -------------------------------
+  // The step's integers (starts, positions, lengths, block tables) were on the device before
+  // the step's first kernel began: they are read before the wait for the kernel before this
+  // one, whose output (q, and this step's keys and values) is not touched until after it.
   // A cluster of `ranks` blocks shares one query tile of one head: each takes a run of its key
   // tiles, and the first block folds the others' outputs into its own at the end.
   const int ranks = SPLIT ? (int)cluster_size() : 1, rank = SPLIT ? (int)cluster_rank() : 0;
@@ -303,6 +305,12 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   float acc[HALF_D];
   float row_max = -FLT_MAX, row_sum = 0.f;
   bool ok = true;
+  // The producer's lane i brings page i of a tile: the first tile's table entries, before the wait.
+  const int last_page = working ? (kv_end - 1) / p.page_size : 0;    // the last page that holds a visible key
+  int first_page = 0;
+  if (warp == 0 && working && lane < BKEYS / p.page_size)
+    first_page = p.block_table[(size_t)b * p.table_width + min(kv_begin / p.page_size + lane, last_page)];
+  dependent_launch_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -319,12 +327,11 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
       }
       const int* table = p.block_table + (size_t)b * p.table_width;
       const int pages_per_tile = BKEYS / p.page_size;
-      const int last_page = (kv_end - 1) / p.page_size;          // the last page that holds a visible key
       const int page_rows_bytes = p.page_size * 128;
       const bool mine = lane < pages_per_tile;
       // A page past the last visible key may not exist: its rows are masked, so any page of
       // the request will do; the last visible one is taken.
-      int page = mine ? table[min(kv_begin / p.page_size + lane, last_page)] : 0;
+      int page = first_page;
       int issued = 0;
       bool ok = true;
       for (int t = 0; t < n_tiles; ++t) {
@@ -720,9 +727,10 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  dependent_launch_wait();
 
   // ---- what this block works on (the same in every role) -------------------------------
+  // The step's integers are read before the wait for the kernel before this one (they were on
+  // the device before the step's first kernel began); q and this step's keys and values after it.
   const int h = blockIdx.x, b = blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
@@ -739,6 +747,14 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
   const int kv_begin = (first_key / BKEYS) * BKEYS;
   const int n_tiles = active ? (kv_end - kv_begin + BKEYS - 1) / BKEYS : 0;
   const int g = h / (p.heads / p.kv_heads);
+  // The producer's lane i brings box i of a tile (a page, or the 64 rows of a larger page that
+  // the tile covers): the first tile's table entries, before the wait.
+  const int box_rows = min(p.page_size, BKEYS);
+  const int last_page = active ? (kv_end - 1) / p.page_size : 0;     // the last page that holds a visible key
+  int first_page = 0;
+  if (warp == 0 && active && lane < BKEYS / box_rows)
+    first_page = p.block_table[(size_t)b * p.table_width + min((kv_begin + lane * box_rows) / p.page_size, last_page)];
+  dependent_launch_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -755,9 +771,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
                       first_token + tile * BQ);
       }
       const int* table = p.block_table + (size_t)b * p.table_width;
-      const int box_rows = min(p.page_size, BKEYS);
       const int boxes = BKEYS / box_rows;
-      const int last_page = (kv_end - 1) / p.page_size;          // the last page that holds a visible key
       const bool mine = lane < boxes;
       // A page past the last visible key may not exist: its rows are masked, so any page of
       // the request will do; the last visible one is taken.
@@ -766,7 +780,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
         const int page = table[min(key / p.page_size, last_page)];
         return (page * p.kv_heads + g) * p.page_size + key % p.page_size;
       };
-      int row = mine ? box_row(0) : 0;
+      int row = mine ? (first_page * p.kv_heads + g) * p.page_size + (kv_begin + lane * box_rows) % p.page_size : 0;
       int issued = 0;
       bool ok = true;
       for (int t = 0; t < n_tiles; ++t) {
