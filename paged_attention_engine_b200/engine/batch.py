@@ -286,7 +286,7 @@ class BatchBuilder:
             token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
             kv_len=part(5), state_slot=part(6), logit_rows=part(7),
             max_q_len=max(q_lens), max_kv_len=width * page if table_width is not None else max_kv,
-            num_single=sum(1 for n in q_lens if n == 1), wants_every_token=rows == list(range(total)), groups=groups,
+            num_single=sum(1 for n in q_lens if n == 1), wants_every_token=len(rows) == total and rows == list(range(total)), groups=groups,
             host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
             sampling=sampling_parts, buffer=dev,
         )
