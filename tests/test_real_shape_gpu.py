@@ -135,3 +135,32 @@ def test_short_portions_after_a_long_one_at_the_real_layer_sizes(folder, dtype_n
         assert have.shape == want[key].shape
         gap = (have - want[key]).abs().max().item()
         assert gap <= helpers.tolerance(dtype, want[key]), f"{dtype_name}/{key}: max |dlogit| {gap:.3e} vs {helpers.tolerance(dtype, want[key]):.3e}"
+
+
+def test_a_long_prompt_whole_then_decoded_at_the_real_layer_sizes(folder):
+    """8,192 tokens in one step (enough blocks that the paired tcgen05 attention is picked), then
+    16 tokens one by one over the 8,192 keys (decode slices and their merge), in bfloat16."""
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.engine.replay import Replayer
+    from paged_attention_engine_b200.kernels import ops
+
+    cfg = plain.read_config(folder)
+    weights = {k: v.float().cuda() for k, v in plain.read_weights(folder).items()}
+    ids = helpers.random_tokens(SHAPE["vocab_size"], 8192 + 16, 9)
+    rows = [0, 127, 128, 4095, 4096, 8191] + list(range(8192, 8192 + 16))
+    hidden = plain.forward_hidden(torch.tensor(ids, device="cuda"), weights, cfg)
+    want = plain.linear(hidden[rows], plain.lm_head_weight(weights)).float().cpu()
+    del weights, hidden
+    torch.cuda.empty_cache()
+
+    engine = Engine.from_pretrained(folder, "bfloat16")
+    replayer = Replayer(engine, max_tokens=8192 + 64, block_size=16)
+    got = [replayer.run({"step": 0, "entries": [{"id": "r", "tokens": ids[:8192], "want": rows[:6]}], "end": []}).float().cpu()]
+    assert ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster() == 0       # the paired kernel
+    for i in range(16):
+        step = {"step": 1 + i, "entries": [{"id": "r", "tokens": [ids[8192 + i]], "want": [0]}], "end": ["r"] if i == 15 else []}
+        got.append(replayer.run(step).float().cpu())
+    ops.check_device_errors()
+    have = torch.cat(got)
+    gap = (have - want).abs().max().item()
+    assert gap <= helpers.tolerance(torch.bfloat16, want), f"max |dlogit| {gap:.3e} vs {helpers.tolerance(torch.bfloat16, want):.3e}"
