@@ -52,6 +52,7 @@ struct Params {
   int rows_b;        // rows of the B operand
   int k_blocks;      // ceil(K / 64)
   int kb_per_split;
+  int planes;        // persistent kernel: K ranges per output tile, each summed into a float32 plane of its own (0 or 1: none)
   int ld_out;        // NORMAL: row pitch of out/residual in elements; SWAPPED: weight rows N
   int out_f32;
   int swiglu;        // NORMAL only: columns come in blocks of 16 gate, 16 up; out[row, n / 2] = silu(gate) * up
@@ -180,14 +181,14 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
 
 // One thread's 16 consecutive outputs of row `row` from column `col0` on: bias, residual,
 // rounding, store (16-byte stores when the row pitch allows).
-__device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, float* v) {
+__device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, float* v, size_t plane_offset = 0) {
     const int valid = min(16, p.rows_b - col0);
     if (p.bias != nullptr) {
 #pragma unroll
       for (int i = 0; i < 16; ++i)
         if (i < valid) v[i] += p.bias[col0 + i];
     }
-    const size_t at = (size_t)row * p.ld_out + col0;
+    const size_t at = plane_offset + (size_t)row * p.ld_out + col0;
     if (p.out_f32) {
       float* out = (float*)p.out + at;
       if (p.residual != nullptr) {
@@ -486,7 +487,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 // tile (tcgen05.ld, bias, residual, rounding, stores) runs while the MMAs of the next tile
 // are issued. Eight warps run it, two for each quarter of the rows: with four the epilogue of
 // a tile (SiLU x up above all) took longer than the tile's MMAs and set the pace. Tiles that share a weight tile are neighbours in the walk, so a weight tile
-// is read from memory once and found in L2 by the other blocks.
+// is read from memory once and found in L2 by the other blocks. When the output has few tiles
+// and K is long, a tile's K is shared out over several blocks, each writing a float32 plane.
 // ---------------------------------------------------------------------------------------
 template <int PBN>
 struct PTile {
@@ -550,16 +552,21 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
   const uint32_t tmem_base = *tmem_holder;
   dependent_launch_wait();
 
-  const int total_tiles = tiles_a * tiles_b;
+  // A work item is an output tile, or one of the `planes` ranges of K of an output tile when a
+  // launch of few tiles and a long K shares each tile out over several blocks.
+  const int planes = p.planes > 1 ? p.planes : 1;
+  const int total_items = tiles_a * tiles_b * planes;
   const int k_blocks = p.k_blocks;
 
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int tile = item / planes, kb_first = (item % planes) * p.kb_per_split;
+        const int kb_end = min(kb_first + p.kb_per_split, k_blocks);
         const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;     // neighbours share the weight tile
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb_first; kb < kb_end; ++kb, ++it) {
           const int s = it % PSTAGES;
           if (it >= PSTAGES && !mbar_wait(empty_bar(s), ((it / PSTAGES) - 1) & 1, abort_flag, p.error, 1)) {
             ok = false;
@@ -589,13 +596,15 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       int local = 0, s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++local) {
         const int acc = local & 1, use = local >> 1;
         if (local >= 2) ok = mbar_wait(tmem_empty_bar(acc), (use - 1) & 1, abort_flag, p.error, 4);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * ACC;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int kb_first = (item % planes) * p.kb_per_split;
+        const int kb_count = min(kb_first + p.kb_per_split, k_blocks) - kb_first;
+        for (int kb = 0; kb < kb_count; ++kb) {
           if (!mbar_try_wait(full_bar(s), phase)) ok = mbar_wait(full_bar(s), phase, abort_flag, p.error, 2);
           if (!ok) break;
           tcgen05_fence_after();
@@ -620,7 +629,9 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
     const int row_in_tile = quadrant * 32 + lane;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++local) {
+      const int tile = item / planes;
+      const size_t plane_offset = (size_t)(item % planes) * p.rows_a * p.ld_out;
       const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
       const int acc = local & 1, use = local >> 1;
       ok = ok && mbar_wait(tmem_full_bar(acc), use & 1, abort_flag, p.error, 3);
@@ -675,7 +686,7 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
           float v[16];
           tmem_load16(lane_address + c0, v);
           const int col0 = tile_b * PBN + c0;
-          if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v);
+          if (row < p.rows_a && col0 < p.rows_b) store_row_chunk(p, row, col0, v, plane_offset);
         }
       }
       tcgen05_fence_before();
@@ -791,14 +802,15 @@ int launch_persistent_with(const Params& p, const void* a, const void* b, int k,
     configured = true;
   }
   const int tiles_a = (p.rows_a + BM - 1) / BM, tiles_b = (p.rows_b + PBN - 1) / PBN;
-  const int blocks = tiles_a * tiles_b < sm_count() ? tiles_a * tiles_b : sm_count();
+  const int items = tiles_a * tiles_b * (p.planes > 1 ? p.planes : 1);
+  const int blocks = items < sm_count() ? items : sm_count();
   launch_kernel(gemm_tcgen05_persistent_kernel<PBN>, dim3(blocks), PERSISTENT_THREADS, T::SMEM_BYTES, stream, map_a, map_b, p, tiles_a, tiles_b);
   return check_launch("linear_tcgen05");
 }
 
 // The tile width whose walk over the output costs least: rounds of tiles over the SMs
 // times (width + a fixed share for a tile's first loads and its epilogue).
-int launch_persistent(const Params& p, const void* a, const void* b, int k, cudaStream_t stream) {
+int persistent_width(const Params& p) {
   const int widths[3] = {256, 192, 176};
   const int tiles_a = (p.rows_a + BM - 1) / BM;
   int best = 256;
@@ -813,6 +825,11 @@ int launch_persistent(const Params& p, const void* a, const void* b, int k, cuda
       best = w;
     }
   }
+  return best;
+}
+
+int launch_persistent(const Params& p, const void* a, const void* b, int k, cudaStream_t stream) {
+  const int best = persistent_width(p);
   if (best == 192) return launch_persistent_with<192>(p, a, b, k, stream);
   if (best == 176) return launch_persistent_with<176>(p, a, b, k, stream);
   return launch_persistent_with<256>(p, a, b, k, stream);
@@ -908,6 +925,47 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
   if (n >= 128) return launch<128, NORMAL>(p, x, w, k, 1, s);
   if (n > 32) return launch<64, NORMAL>(p, x, w, k, 1, s);
   return launch<32, NORMAL>(p, x, w, k, 1, s);
+}
+
+// How many float32 planes `pae_linear_tcgen05_planes` writes for this shape: 1 (call
+// `pae_linear_tcgen05` instead) unless the output has so few tiles that they leave more than
+// half of the SMs idle while K is long (a down projection for a few hundred tokens): then
+// each tile's K is shared out over as many blocks as fill the SMs, 8 k-blocks each at least.
+PAE_EXPORT int pae_linear_tcgen05_plane_count(int tokens, int n, int k) {
+  const int k_blocks = (k + BK - 1) / BK;
+  if (tokens <= 64 || n < 256 || k_blocks < 32) return 1;
+  Params p{};
+  p.rows_a = tokens;
+  p.rows_b = n;
+  const int width = persistent_width(p);
+  const int tiles = ((tokens + BM - 1) / BM) * ((n + width - 1) / width);
+  if (tiles * 2 > sm_count()) return 1;
+  int planes = sm_count() / tiles;
+  planes = planes > k_blocks / 8 ? k_blocks / 8 : planes;
+  if (planes < 2) return 1;
+  const int per = (k_blocks + planes - 1) / planes;
+  return (k_blocks + per - 1) / per;
+}
+
+// partial[plane, token, n] (float32) = x[tokens, k_range(plane)] . w[n, k_range(plane)]^T with
+// planes = pae_linear_tcgen05_plane_count(tokens, n, k) > 1; the caller adds the planes up.
+PAE_EXPORT int pae_linear_tcgen05_planes(float* partial, const void* x, const void* w, int tokens, int n, int k, int planes,
+                                         int* error, void* stream) {
+  if (tokens == 0 || n == 0) return 0;
+  if (int err = check_operands(x, w, k)) return err;
+  if (planes < 2 || planes != pae_linear_tcgen05_plane_count(tokens, n, k))
+    return fail(2, "linear_tcgen05_planes: %d planes for [%d, %d] x [%d, %d]", planes, tokens, k, n, k);
+  Params p{};
+  p.out = partial;
+  p.rows_a = tokens;
+  p.rows_b = n;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = (p.k_blocks + planes - 1) / planes;
+  p.planes = planes;
+  p.ld_out = n;
+  p.out_f32 = 1;
+  p.error = error;
+  return launch_persistent(p, x, w, k, (cudaStream_t)stream);
 }
 
 // How many float32 partial planes `pae_linear_tcgen05_swapped` writes for this shape.

@@ -290,6 +290,15 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch
             return partial[0]
         pending = PendingSum(partial, bias, residual, out_dtype)
         return pending if fuse_split_sums else materialized(pending)
+    planes = lib.pae_linear_tcgen05_plane_count(c_int(m), c_int(n), c_int(k))
+    if planes > 1:
+        # Few output tiles and a long K (a down projection for a few hundred tokens): each
+        # tile's K is shared out over several blocks, whose float32 planes are added up later.
+        partial = torch.empty((planes, m, n), dtype=torch.float32, device=x.device)
+        _check(lib, lib.pae_linear_tcgen05_planes(_ptr(partial), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
+                                                  c_int(planes), _ptr(flag), _stream()))
+        pending = PendingSum(partial, bias, residual, out_dtype)
+        return pending if fuse_split_sums else materialized(pending)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
                                        c_int(k), out_f32, _ptr(flag), _stream()))

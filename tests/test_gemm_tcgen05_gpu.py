@@ -50,6 +50,25 @@ def test_many_tokens(ops, m, n, k, extras):
     _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
 
 
+@pytest.mark.parametrize("m,n,k,planes", [(65, 1536, 8960, 16), (128, 1536, 8960, 16), (300, 1536, 8960, 5), (1024, 1536, 8960, 2),
+                                          (130, 520, 2056, 4), (2048, 1536, 8960, 1), (128, 1536, 1536, 1)])
+@pytest.mark.parametrize("extras", [(False, False), (True, True)])
+def test_few_output_tiles_and_a_long_k_share_k_over_blocks(ops, m, n, k, planes, extras):
+    """A down projection for a few hundred tokens has a handful of output tiles: each tile's K
+    is shared out over blocks that write float32 planes, which the consumer adds up. The plane
+    count is what fills the SMs (for 148 of them), 1 when the tiles do already or K is short."""
+    lib = ops._lib("gemm_tcgen05")
+    import ctypes
+    assert lib.pae_linear_tcgen05_plane_count(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k)) == planes
+    x = _rand((m, k), 1)
+    w = _rand((n, k), 2, 0.05)
+    pending = ops.linear(x, w)
+    assert isinstance(pending, ops.PendingSum) == (planes > 1)
+    if planes > 1:
+        assert tuple(pending.partial.shape) == (planes, m, n)
+    _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
+
+
 @pytest.mark.parametrize("m,n,k", [(4, 151936, 1536), (70, 3001, 520), (8, 509, 96)])
 def test_float32_logits(ops, m, n, k):
     _check(ops, m, n, k, bias=False, residual=False, out_dtype=torch.float32)
