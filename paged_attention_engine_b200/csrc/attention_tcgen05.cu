@@ -849,7 +849,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
       if (n_tiles > 0) issue_scores(0);
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (t + 1 < n_tiles) issue_scores(t + 1);
-        const int st = t & 1, stage = t % KV_STAGES;
+        const int stage = t % KV_STAGES;
         ok = ok && mbar_wait(bar(V_FULL, stage), (t / KV_STAGES) & 1, abort_flag, p.error, 5);
         ok = ok && mbar_wait(bar(P_READY), t & 1, abort_flag, p.error, 6);
         if (!ok) break;

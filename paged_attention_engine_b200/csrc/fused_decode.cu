@@ -80,8 +80,6 @@ __global__ void __launch_bounds__(512) splitk_rms_norm_kernel(T* __restrict__ no
     normed[(size_t)row * width + i] = from_float<T>(row_values[i] * scale * weight[i]);
 }
 
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-
 // Four neighbouring values of T as floats, and back (16- or 8-byte accesses).
 __device__ __forceinline__ void load4(const float* p, float* v) {
   const float4 t = *(const float4*)p;
