@@ -212,7 +212,12 @@ def time_end_to_end(engine, batch: int, steps: int, warmup: int, torch):
 
     # Prompts are cut into portions under the token budget, so requests start to decode a few
     # steps apart; SLACK extra tokens keep every request alive through the timed steps.
+    # The prefill of 8 x 4,000 tokens runs at the power cap, and the decode steps right after it
+    # are 3 to 6 % slower than steady ones for about 60 ms (measured: windows of 64 steps after
+    # 8, 16 and 48 warm-up steps take 1.42, 1.38 and 1.35 ms a step, later windows 1.35): the
+    # warm-up is at least 48 steps.
     SLACK = 8
+    warmup = max(warmup, 48)
     prompt_len = CONTEXT - (warmup + steps) - SLACK - 1
     llm = LLM(
         engine, num_blocks=batch * (CONTEXT // BLOCK_SIZE + 1) + 8, block_size=BLOCK_SIZE,
