@@ -97,6 +97,10 @@ class BlockAllocator:
         """A copy of the table; released leading blocks read HOLE (-1)."""
         return tuple(self._tables[seq_id].blocks)
 
+    def table_len(self, seq_id) -> int:
+        """Entries of the table, released leading ones included."""
+        return len(self._tables[seq_id].blocks)
+
     def num_tokens(self, seq_id) -> int:
         return self._tables[seq_id].tokens
 

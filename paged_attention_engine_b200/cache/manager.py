@@ -179,9 +179,10 @@ class CacheManager:
         `margin_blocks` free in every pool?"""
         if key is None and self.slots.num_free == 0:
             return False
-        return all(
-            a.blocks_to_append(key, count) + margin_blocks <= a.num_free for a in self.allocators
-        )
+        for a in self.allocators:
+            if a.blocks_to_append(key, count) + margin_blocks > a.num_free:
+                return False
+        return True
 
     # -- lifecycle -------------------------------------------------------- #
 
@@ -201,17 +202,20 @@ class CacheManager:
     def reserve(self, key: Hashable, count: int) -> AllocResult:
         """Room for `count` more tokens in every group, or in none."""
         live = self._live[key]
-        if not self.can_append(key, count, 0):
+        # One pool takes all of the blocks or none by itself; several are asked first.
+        if len(self.allocators) != 1 and not self.can_append(key, count, 0):
             return AllocResult(AllocStatus.OUT_OF_BLOCKS)
-        taken: list[int] = []
+        first = AllocResult(AllocStatus.OK)
         for g, a in enumerate(self.allocators):
-            before = len(a.block_table(key))
+            before = a.table_len(key)
             result = a.append_tokens(key, count)
-            assert result.ok
+            if not result.ok:
+                assert len(self.allocators) == 1
+                return result
             self._write_table(g, live.slot, before, result.new_block_ids)
             if g == 0:
-                taken = list(result.new_block_ids)
-        return AllocResult(AllocStatus.OK, tuple(taken))
+                first = result
+        return first
 
     def _write_table(self, g: int, slot: int, start: int, ids: Sequence[int]) -> None:
         if not ids:
