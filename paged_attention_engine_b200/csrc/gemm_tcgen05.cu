@@ -184,9 +184,17 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
 __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, float* v, size_t plane_offset = 0) {
     const int valid = min(16, p.rows_b - col0);
     if (p.bias != nullptr) {
+      if (valid == 16 && (((uintptr_t)(p.bias + col0)) & 15) == 0) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if (i < valid) v[i] += p.bias[col0 + i];
+        for (int q = 0; q < 4; ++q) {
+          const float4 b = *(const float4*)(p.bias + col0 + 4 * q);
+          v[4 * q] += b.x; v[4 * q + 1] += b.y; v[4 * q + 2] += b.z; v[4 * q + 3] += b.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (i < valid) v[i] += p.bias[col0 + i];
+      }
     }
     const size_t at = plane_offset + (size_t)row * p.ld_out + col0;
     if (p.out_f32) {
@@ -271,16 +279,41 @@ __device__ __forceinline__ void store_swiglu_chunk(const Params& p, int row, int
 // stand d/2 further, of token `row`. Bias, rounding to bfloat16, rotation of q and k
 // (engine/model.py:155-161: lo' = lo c - hi s, hi' = hi c + lo s), then qkv and, for k and v,
 // the token's place in its page. The same arithmetic as the stand-alone kernels.
+// The cosines and sines of 16 frequencies from `f0` on of token `row`.
+__device__ __forceinline__ void load_angles(const Params& p, int row, int f0, float* cs, float* sn) {
+  const int d = p.head_dim;
+  const float4* cos4 = (const float4*)(p.rotary_table + (size_t)row * d + f0);
+  const float4* sin4 = (const float4*)(p.rotary_table + (size_t)row * d + (d >> 1) + f0);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float4 c = cos4[q], sv = sin4[q];
+    cs[q * 4] = c.x; cs[q * 4 + 1] = c.y; cs[q * 4 + 2] = c.z; cs[q * 4 + 3] = c.w;
+    sn[q * 4] = sv.x; sn[q * 4 + 1] = sv.y; sn[q * 4 + 2] = sv.z; sn[q * 4 + 3] = sv.w;
+  }
+}
+
 __device__ __forceinline__ void store_rotary_chunks(const Params& p, int row, int head, int f0, float* lo, float* hi,
-                                                    const float* cs, const float* sn) {
+                                                    const float* cs, const float* sn, int slot) {
   const int d = p.head_dim, half = d >> 1;
   const int col_lo = head * d + f0, col_hi = col_lo + half;
+  if (p.bias != nullptr) {
+    if (((uintptr_t)(p.bias + col_lo) & 15) == 0 && ((uintptr_t)(p.bias + col_hi) & 15) == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 a = *(const float4*)(p.bias + col_lo + 4 * q), b = *(const float4*)(p.bias + col_hi + 4 * q);
+        lo[4 * q] += a.x; lo[4 * q + 1] += a.y; lo[4 * q + 2] += a.z; lo[4 * q + 3] += a.w;
+        hi[4 * q] += b.x; hi[4 * q + 1] += b.y; hi[4 * q + 2] += b.z; hi[4 * q + 3] += b.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        lo[i] += p.bias[col_lo + i];
+        hi[i] += p.bias[col_hi + i];
+      }
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    if (p.bias != nullptr) {
-      lo[i] += p.bias[col_lo + i];
-      hi[i] += p.bias[col_hi + i];
-    }
     lo[i] = __bfloat162float(__float2bfloat16_rn(lo[i]));
     hi[i] = __bfloat162float(__float2bfloat16_rn(hi[i]));
   }
@@ -302,8 +335,7 @@ __device__ __forceinline__ void store_rotary_chunks(const Params& p, int row, in
   *(uint4*)(out + col_lo + 8) = packed[1];
   *(uint4*)(out + col_hi) = packed[2];
   *(uint4*)(out + col_hi + 8) = packed[3];
-  if (head >= p.heads && p.slots != nullptr) {
-    const int slot = p.slots[row];
+  if (head >= p.heads) {
     if (slot >= 0) {
       const int page = slot / p.page_size, offset = slot - page * p.page_size;
       const bool is_key = head < p.heads + p.kv_heads;
@@ -634,11 +666,18 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       const size_t plane_offset = (size_t)(item % planes) * p.rows_a * p.ld_out;
       const int tile_a = tile % tiles_a, tile_b = tile / tiles_a;
       const int acc = local & 1, use = local >> 1;
+      const int row = tile_a * BM + row_in_tile;
+      // What the rotation needs of this thread's token is asked for before the wait for the
+      // tile's MMAs: its place in its page and its first 16 cosines and sines.
+      const bool rotating = p.rotary && p.rotary_table != nullptr && row < p.rows_a;
+      float cs_a[16], sn_a[16];
+      int slot = -1;
+      if (rotating) load_angles(p, row, 0, cs_a, sn_a);
+      if (p.rotary && p.slots != nullptr && row < p.rows_a) slot = p.slots[row];
       ok = ok && mbar_wait(tmem_full_bar(acc), use & 1, abort_flag, p.error, 3);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = tile_a * BM + row_in_tile;
       const uint32_t lane_address = tmem_base + ((uint32_t)(quadrant * 32) << 16) + acc * ACC;
       // The warps of a quarter of the rows share the tile's columns in equal ranges that end
       // on a multiple of 32 columns (a gate block with its up block) or of the head size.
@@ -647,28 +686,28 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
       const int col_begin = min(share * range, PBN), col_end = min(col_begin + range, PBN);
       if (p.rotary) {
         // 16 columns of each half of a head at a time; the token's cosines and sines of those
-        // 16 frequencies are read once and serve every head of the tile.
+        // 16 frequencies are read once and serve every head of the tile, and those of the next
+        // 16 are on their way while these are used.
         const int d = p.head_dim, half = d >> 1;
-#pragma unroll 1
-        for (int f0 = 0; f0 < half; f0 += 16) {
-          float cs[16], sn[16];
-          if (p.rotary_table != nullptr && row < p.rows_a) {
-            const float4* cos4 = (const float4*)(p.rotary_table + (size_t)row * d + f0);
-            const float4* sin4 = (const float4*)(p.rotary_table + (size_t)row * d + half + f0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float4 c = cos4[q], sv = sin4[q];
-              cs[q * 4] = c.x; cs[q * 4 + 1] = c.y; cs[q * 4 + 2] = c.z; cs[q * 4 + 3] = c.w;
-              sn[q * 4] = sv.x; sn[q * 4 + 1] = sv.y; sn[q * 4 + 2] = sv.z; sn[q * 4 + 3] = sv.w;
-            }
-          }
+        auto heads_of = [&](int f0, const float* cs, const float* sn) {
 #pragma unroll 1
           for (int head0 = col_begin; head0 < col_end; head0 += d) {
             float lo[16], hi[16];
             tmem_load16(lane_address + head0 + f0, lo);
             tmem_load16(lane_address + head0 + half + f0, hi);
             if (row < p.rows_a && tile_b * PBN + head0 < p.rows_b)
-              store_rotary_chunks(p, row, (tile_b * PBN + head0) / d, f0, lo, hi, cs, sn);
+              store_rotary_chunks(p, row, (tile_b * PBN + head0) / d, f0, lo, hi, cs, sn, slot);
+          }
+        };
+#pragma unroll 1
+        for (int f0 = 0; f0 < half; f0 += 32) {
+          float cs_b[16], sn_b[16];
+          const bool second = f0 + 16 < half;
+          if (second && rotating) load_angles(p, row, f0 + 16, cs_b, sn_b);
+          heads_of(f0, cs_a, sn_a);
+          if (second) {
+            if (f0 + 32 < half && rotating) load_angles(p, row, f0 + 32, cs_a, sn_a);
+            heads_of(f0 + 16, cs_b, sn_b);
           }
         }
       } else if (p.swiglu) {
