@@ -77,10 +77,13 @@ def _ptr(t: torch.Tensor | None):
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream():
     """The current stream's handle (asked for at every launch: the quick way when torch has it)."""
-    if _raw_stream is not None:
-        return c_void_p(_raw_stream(torch.cuda.current_device()))
+    if _raw_stream is not None and _get_device is not None:
+        return c_void_p(_raw_stream(_get_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
