@@ -22,7 +22,7 @@ from typing import Hashable, Sequence
 import numpy as np
 
 from ..config.model_spec import ModelSpec
-from ..parts.base import MIXERS, CacheNeed, StateNeed
+from ..parts.base import REGISTRIES, CacheNeed, StateNeed, layer_part_specs
 from .allocator import HOLE, AllocResult, AllocStatus, BlockAllocator
 
 
@@ -43,6 +43,34 @@ class CachePlan:
     entry_writes: dict             # schedule position -> bool
     state_needs: dict              # schedule position -> StateNeed
 
+    def bytes_per_block(self, block_size: int, element_size: int) -> int:
+        """Bytes of one page id: its keys and values in every entry of every group (each group
+        has a pool of its own with the same number of pages)."""
+        return sum(2 * len(g.entries) * g.num_kv_heads * g.head_dim * block_size * element_size for g in self.groups)
+
+
+def layer_needs(layer) -> tuple[CacheNeed | None, StateNeed | None]:
+    """What a layer's parts need of the cache: pages (keys and values) and per-request state.
+    Whichever part declares a need gets the schedule entry's `EntryCache` from its block; one
+    part per layer may need pages and one may need state (a layer with two such mixers is two
+    layers in the schedule)."""
+    pages, states = [], []
+    for role, registry, part in layer_part_specs(layer):
+        cls = REGISTRIES[registry].get(part.kind)
+        need = getattr(cls, "cache_need", lambda _spec: None)(part)
+        state = getattr(cls, "state_need", lambda _spec: None)(part)
+        if need is not None:
+            pages.append((role, need))
+        if state is not None:
+            states.append((role, state))
+    for what, found in (("pages", pages), ("per-request state", states)):
+        if len(found) > 1:
+            raise ValueError(
+                f"a '{layer.block}' layer has {len(found)} parts that need {what} ({', '.join(r for r, _ in found)}); "
+                "one schedule entry has one cache: put them in layers of their own"
+            )
+    return (pages[0][1] if pages else None), (states[0][1] if states else None)
+
 
 def plan_cache(spec: ModelSpec) -> CachePlan:
     """Groups the schedule's entries by what their mixers need of the cache."""
@@ -50,11 +78,8 @@ def plan_cache(spec: ModelSpec) -> CachePlan:
     state_needs: dict[int, StateNeed] = {}
     needs: dict[int, CacheNeed | None] = {}
     for pos, entry in enumerate(spec.schedule):
-        mixer = spec.layers[entry.layer].mixer
-        cls = MIXERS.get(mixer.kind)
-        need = cls.cache_need(mixer)
+        need, state = layer_needs(spec.layers[entry.layer])
         needs[pos] = need
-        state = cls.state_need(mixer)
         if state is not None:
             state_needs[pos] = state
         if entry.cache_from is None and need is not None:

@@ -31,7 +31,9 @@ def _engine_options(parser: argparse.ArgumentParser) -> None:
     source.add_argument("--random", metavar="CONFIG", help="a config.json: the model gets random weights (see --weights-seed)")
     parser.add_argument("--weights-seed", type=int, default=0, help="seed of the random weights of --random")
     parser.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
-    parser.add_argument("--num-blocks", type=int, default=3584, help="pages of the cache pool (reference: 3584)")
+    parser.add_argument("--num-blocks", type=int, default=None, help="pages of the cache pool (reference: 3584, the default)")
+    parser.add_argument("--kv-gb", type=float, default=None,
+                        help="size the cache pool by bytes instead: as many pages as this many GB (1e9 bytes) pay for")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per page (reference: 16)")
     parser.add_argument("--max-num-seqs", type=int, default=64)
     parser.add_argument("--max-num-batched-tokens", type=int, default=8192)
@@ -43,6 +45,7 @@ def _llm(args, max_num_seqs=None):
 
     options = dict(
         dtype=args.dtype, num_blocks=args.num_blocks, block_size=args.block_size,
+        kv_bytes=int(args.kv_gb * 1e9) if args.kv_gb is not None else None,
         max_num_seqs=max_num_seqs or args.max_num_seqs, max_num_batched_tokens=args.max_num_batched_tokens,
         admission_margin_blocks=args.admission_margin_blocks,
     )

@@ -8,7 +8,8 @@ builder and, if it needs them, new parts; nothing else changes.
 
 A part is named by its registry key (`kind`) and carries its sizes and constants
 as `params`; no part knows which model it is in. Layers may differ from one
-another in every part. The order in which layers run is the `schedule`: a list
+another in every part, and in which parts they have: a layer is a block kind plus
+the parts that this kind declares, by role. The order in which layers run is the `schedule`: a list
 of entries that may name a layer twice (its weights are then shared, each run has
 a cache of its own) or let an entry read the cache that an earlier entry wrote.
 """
@@ -41,13 +42,23 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a mixer and a feed-forward, each with its norm, arranged by `block`."""
+    """One layer: a block kind and the parts it arranges, by role.
+
+    Which roles a layer has, and from which registry each part comes, is the block
+    kind's own declaration (`roles` of the class registered under `block`): the usual
+    decoder block has `mixer_norm`, `mixer`, `feed_forward_norm` and `feed_forward`;
+    a block with four norms or one shared norm names its roles otherwise and nothing
+    outside that class changes. `layer.mixer` reads `layer.parts["mixer"]`.
+    """
 
     block: str
-    mixer_norm: PartSpec
-    mixer: PartSpec
-    feed_forward_norm: PartSpec
-    feed_forward: PartSpec
+    parts: Mapping[str, PartSpec]
+
+    def __getattr__(self, role: str) -> PartSpec:
+        parts = object.__getattribute__(self, "parts")
+        if role in parts:
+            return parts[role]
+        raise AttributeError(f"a '{object.__getattribute__(self, 'block')}' layer has no part '{role}'; it has: {', '.join(parts)}")
 
 
 @dataclass(frozen=True)

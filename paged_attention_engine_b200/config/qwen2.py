@@ -17,9 +17,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Mapping
 
-
-class ConfigError(ValueError):
-    """A config.json that this architecture cannot run; the message names the key."""
+from .errors import ConfigError
 
 
 def _need(raw: Mapping[str, Any], key: str, kind):

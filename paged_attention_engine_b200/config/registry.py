@@ -14,8 +14,9 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping
 
+from .errors import ConfigError
 from .model_spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
-from .qwen2 import ConfigError, Qwen2Config
+from .qwen2 import Qwen2Config
 
 
 @dataclass(frozen=True)
@@ -65,8 +66,7 @@ def qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
         prefix = f"model.layers.{i}"
         norm = {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}
         layers.append(
-            LayerSpec(
-                block="pre_norm_residual",
+            LayerSpec("pre_norm_residual", dict(
                 mixer_norm=PartSpec("rms_norm", norm, f"{prefix}.input_layernorm"),
                 mixer=PartSpec(
                     "gqa_attention",
@@ -88,7 +88,7 @@ def qwen2_spec(cfg: Qwen2Config) -> ModelSpec:
                     {"hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size},
                     f"{prefix}.mlp",
                 ),
-            )
+            ))
         )
     return ModelSpec(
         architecture=cfg.architecture,

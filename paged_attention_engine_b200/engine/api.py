@@ -13,47 +13,50 @@ from __future__ import annotations
 from pathlib import Path
 from typing import Any, Mapping, Sequence
 
+from ..config.engine_config import ADMISSION_MARGIN_BLOCKS, BLOCK_SIZE, NUM_GPU_BLOCKS, EngineConfig
 from .executor import ModelExecutor
 from .llm import Engine
-from .scheduler import ADMISSION_MARGIN_BLOCKS, Request, Scheduler, StepResult
+from .scheduler import Request, Scheduler, StepResult
 
-# The reference's pool: 3584 blocks of 16 tokens (engine/cache.py:29-30).
-BLOCK_SIZE = 16
-NUM_GPU_BLOCKS = 3584
+__all__ = ["ADMISSION_MARGIN_BLOCKS", "BLOCK_SIZE", "NUM_GPU_BLOCKS", "EngineConfig", "LLM"]
 
 
 class LLM:
-    def __init__(
-        self,
-        engine: Engine,
-        num_blocks: int = NUM_GPU_BLOCKS,
-        block_size: int = BLOCK_SIZE,
-        max_num_seqs: int | None = 64,
-        max_num_batched_tokens: int | None = 8192,
-        admission_margin_blocks: int = ADMISSION_MARGIN_BLOCKS,
-        record_logits: bool = False,
-        use_graphs: bool = True,
-        asynchronous: bool | None = None,
-    ) -> None:
+    """`LLM(engine, EngineConfig(...))`, or the same options as keywords
+    (`LLM(engine, num_blocks=..., max_num_seqs=...)`)."""
+
+    def __init__(self, engine: Engine, config: EngineConfig | None = None, **options: Any) -> None:
+        if config is not None and options:
+            raise TypeError("give an EngineConfig or keyword options, not both")
+        if config is None:
+            options.setdefault("dtype", str(engine.dtype).replace("torch.", ""))
+            config = EngineConfig.from_options(options)
+        self.config = config
         self.engine = engine
-        slots = max_num_seqs if max_num_seqs is not None else 256
-        self.cache = engine.new_paged_cache(num_blocks, block_size, slots)
-        self.runner = engine.new_runner(self.cache, use_graphs)
-        self.executor = ModelExecutor(self.runner, asynchronous)
+        self.num_blocks = config.pool_blocks(engine.bytes_per_block(config.block_size))
+        slots = config.max_num_seqs if config.max_num_seqs is not None else 256
+        self.cache = engine.new_paged_cache(self.num_blocks, config.block_size, slots)
+        self.runner = engine.new_runner(self.cache, config.use_graphs)
+        self.executor = ModelExecutor(self.runner, config.asynchronous, default_seed=config.seed)
         self.scheduler = Scheduler(
-            self.executor, self.cache.manager, admission_margin_blocks=admission_margin_blocks,
-            record_logits=record_logits, max_num_seqs=max_num_seqs, max_num_batched_tokens=max_num_batched_tokens,
-            max_model_len=engine.spec.max_positions,
+            self.executor, self.cache.manager, admission_margin_blocks=config.admission_margin_blocks,
+            record_logits=config.record_logits, max_num_seqs=config.max_num_seqs,
+            max_num_batched_tokens=config.max_num_batched_tokens, max_model_len=engine.spec.max_positions,
         )
 
     @classmethod
-    def from_pretrained(cls, folder: str | Path, dtype="bfloat16", device="cuda:0", **options) -> "LLM":
-        return cls(Engine.from_pretrained(folder, dtype, device), **options)
+    def from_pretrained(cls, folder: str | Path, dtype=None, device="cuda:0", config: EngineConfig | None = None,
+                        **options) -> "LLM":
+        dtype = dtype or (config.dtype if config is not None else options.get("dtype", "bfloat16"))
+        options.pop("dtype", None)
+        return cls(Engine.from_pretrained(folder, dtype, device), config, **options)
 
     @classmethod
-    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype="bfloat16", device="cuda:0",
-                    as_written: bool = False, **options) -> "LLM":
-        return cls(Engine.from_random(raw_config, seed, dtype, device, as_written=as_written), **options)
+    def from_random(cls, raw_config: Mapping[str, Any], seed: int = 0, dtype=None, device="cuda:0",
+                    as_written: bool = False, config: EngineConfig | None = None, **options) -> "LLM":
+        dtype = dtype or (config.dtype if config is not None else options.get("dtype", "bfloat16"))
+        options.pop("dtype", None)
+        return cls(Engine.from_random(raw_config, seed, dtype, device, as_written=as_written), config, **options)
 
     def add_request(self, request: Request) -> bool:
         return self.scheduler.add_request(request)

@@ -37,8 +37,9 @@ class ModelExecutor:
     sampled tokens stay on the device, feed the next step there, and reach the host a step
     later through a `_TokenFuture`. With `record_logits` the step is read back at once."""
 
-    def __init__(self, runner: ModelRunner, asynchronous: bool | None = None) -> None:
+    def __init__(self, runner: ModelRunner, asynchronous: bool | None = None, default_seed: int = 0) -> None:
         self.runner = runner
+        self.default_seed = int(default_seed)
         self.manager = runner.manager
         on_gpu = runner.runtime.device.type == "cuda"
         self.asynchronous = on_gpu if asynchronous is None else (asynchronous and on_gpu)
@@ -66,7 +67,8 @@ class ModelExecutor:
             if w.wants_token:
                 request = w.seq.request
                 rows.append(
-                    SamplingRow(request.temperature, request.seed or 0, request.sampling_key, len(w.seq.generated))
+                    SamplingRow(request.temperature, self.default_seed if request.seed is None else request.seed,
+                                request.sampling_key, len(w.seq.generated))
                 )
         output = self.runner.step(entries, rows if rows else None)
         results = [WorkResult(None) for _ in work]

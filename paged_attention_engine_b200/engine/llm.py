@@ -87,6 +87,11 @@ class Engine:
         manager = CacheManager(self.cache_plan.groups, num_blocks, block_size, max_num_seqs)
         return PagedKVCache(self.cache_plan, manager, self.dtype, self.device)
 
+    def bytes_per_block(self, block_size: int = 16) -> int:
+        """Device bytes behind one page id (the reference: 2 x layers x kv heads x head size x
+        element size per token, bench/baseline.py:78-90)."""
+        return self.cache_plan.bytes_per_block(block_size, torch.empty((), dtype=self.dtype).element_size())
+
     def new_runner(self, cache: PagedKVCache, use_graphs: bool = True) -> ModelRunner:
         return ModelRunner(self.model, cache, use_graphs)
 
@@ -94,21 +99,25 @@ class Engine:
     def vocab_size(self) -> int:
         return self.spec.vocab_size
 
-    def weight_bytes(self) -> int:
-        """Bytes of every distinct weight tensor that a step reads."""
+    def weight_bytes(self, num_tokens: int = 1) -> int:
+        """Bytes of the weights that a step of `num_tokens` tokens reads: every distinct tensor
+        that a part holds, once. A part that reads only some of what it holds (experts chosen by
+        a router) says so itself with `step_weight_bytes(num_tokens)`."""
         seen: dict[int, int] = {}
+        extra = 0
 
         def visit(obj: Any) -> None:
+            nonlocal extra
+            own = getattr(obj, "step_weight_bytes", None)
+            if own is not None:
+                extra += int(own(num_tokens))
+                return
             for value in vars(obj).values():
                 if isinstance(value, torch.Tensor):
                     seen[value.data_ptr()] = value.numel() * value.element_size()
                 elif hasattr(value, "runtime") and value is not obj:
                     visit(value)
 
-        model = self.model
-        for part in (model.embedding, model.head, model.final_norm):
+        for part in self.model.parts():
             visit(part)
-        for layer in model.layers:
-            for part in (layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward):
-                visit(part)
-        return sum(seen.values())
+        return sum(seen.values()) + extra

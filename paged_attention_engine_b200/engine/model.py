@@ -10,22 +10,23 @@ batched step from a loop over requests.
 
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Any
 
 import torch
 
 from ..config.model_spec import ModelSpec
-from ..parts.base import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, Runtime
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, REGISTRIES, Runtime, layer_part_specs
 
 
-@dataclass
 class Layer:
-    block: Any
-    mixer_norm: Any
-    mixer: Any
-    feed_forward_norm: Any
-    feed_forward: Any
+    """A layer as it runs: the block and the parts that the block kind declares, each under
+    its role's name (`layer.mixer`, `layer.mixer_norm`, ...)."""
+
+    def __init__(self, block: Any, parts: dict[str, Any]) -> None:
+        self.block = block
+        self.parts = parts
+        for role, part in parts.items():
+            setattr(self, role, part)
 
 
 class DecoderModel:
@@ -38,20 +39,20 @@ class DecoderModel:
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, tensors, runtime)
         self.layers: list[Layer] = []
         for layer in spec.layers:
-            self.layers.append(
-                Layer(
-                    block=BLOCKS.get(layer.block)(),
-                    mixer_norm=NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, tensors, runtime),
-                    mixer=MIXERS.get(layer.mixer.kind)(layer.mixer, tensors, runtime),
-                    feed_forward_norm=NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, tensors, runtime),
-                    feed_forward=FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, tensors, runtime),
-                )
-            )
+            built = {
+                role: REGISTRIES[registry].get(part.kind)(part, tensors, runtime)
+                for role, registry, part in layer_part_specs(layer)
+            }
+            self.layers.append(Layer(BLOCKS.get(layer.block)(), built))
         self.forward_pass_count = 0
-        parts = [self.embedding, self.head, self.final_norm]
+        self.graph_safe = all(getattr(part, "graph_safe", True) for part in self.parts())
+
+    def parts(self) -> list[Any]:
+        """Every part of the model, blocks included (parts nested inside others are theirs)."""
+        out = [self.embedding, self.head, self.final_norm]
         for layer in self.layers:
-            parts += [layer.block, layer.mixer_norm, layer.mixer, layer.feed_forward_norm, layer.feed_forward]
-        self.graph_safe = all(getattr(part, "graph_safe", True) for part in parts)
+            out += [layer.block, *layer.parts.values()]
+        return out
 
     def forward(self, ctx, entry_caches) -> torch.Tensor | None:
         """Runs the step's tokens through every schedule entry; float32 logits

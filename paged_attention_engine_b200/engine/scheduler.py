@@ -75,7 +75,7 @@ class Event:
 @dataclass(frozen=True)
 class Request:
     """What a user asks for. `temperature` 0 is greedy; `seed` makes a temperature draw
-    repeatable (None: seed 0)."""
+    repeatable (None: the engine's seed, 0 unless its options say otherwise)."""
 
     request_id: str
     prompt_token_ids: tuple[int, ...]

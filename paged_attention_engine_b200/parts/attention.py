@@ -13,7 +13,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model_spec import PartSpec
-from .base import MIXERS, POSITION_ENCODINGS, CacheNeed, Part, TensorSpec
+from .base import MIXERS, CacheNeed, Part, TensorSpec
 
 
 @MIXERS.register("gqa_attention")
@@ -34,6 +34,13 @@ class GQAAttention(Part):
                 out.append(TensorSpec(spec.tensor_name(f"{name}.bias"), (rows,), "vector"))
         out.append(TensorSpec(spec.tensor_name("o_proj.weight"), (hidden, nq), "matrix"))
         return out
+
+    @classmethod
+    def sub_parts(cls, spec: PartSpec) -> list[tuple[str, PartSpec]]:
+        enc = spec.params.get("position_encoding")
+        if enc is None:
+            return []
+        return [("position_encoding", PartSpec(enc["kind"], {k: v for k, v in enc.items() if k != "kind"}, spec.prefix))]
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed:
@@ -57,11 +64,8 @@ class GQAAttention(Part):
         if p.get("qkv_bias", False):
             self.qkv_bias = torch.cat([tensors.pop(spec.tensor_name(f"{n}.bias")) for n in names], dim=0).contiguous()
         self.o_weight = tensors.pop(spec.tensor_name("o_proj.weight"))
-        enc = p.get("position_encoding")
-        self.position_encoding = None
-        if enc is not None:
-            enc_spec = PartSpec(enc["kind"], {k: v for k, v in enc.items() if k != "kind"})
-            self.position_encoding = POSITION_ENCODINGS.get(enc["kind"])(enc_spec, tensors, runtime)
+        built = self.build_sub_parts(tensors)
+        self.position_encoding = built[0] if built else None
 
     def forward(self, ctx, x, residual, cache):
         ops = self.ops

@@ -12,7 +12,11 @@ What each kind of part must provide:
 
   every part    `tensor_specs(spec)`: the tensors it reads from the checkpoint
                 (full names, shapes, kind), used by the loader's validation and by
-                the random-weights mode; `__init__(spec, tensors, runtime)`.
+                the random-weights mode; `__init__(spec, tensors, runtime)`;
+                `sub_parts(spec)`: the parts it holds inside itself (an attention's
+                position encoding), as (registry name, PartSpec) pairs: the loader
+                and the random-weights mode follow them, so a part with parts of
+                its own needs no line anywhere else.
   norm          `forward(ctx, x) -> y`, same shape.
   position enc. `table(ctx)`: whatever its mixers need for this step's positions,
                 computed once per step and memoised in `ctx.memo`.
@@ -23,7 +27,12 @@ What each kind of part must provide:
                 `forward(ctx, x, residual, cache) -> residual + mixer(x)` where
                 `cache` is the `EntryCache` of the schedule entry that runs.
   feed-forward  `forward(ctx, x, residual) -> residual + ff(x)`.
-  block         `forward(ctx, hidden, layer, cache) -> hidden`.
+  block         `roles`: which parts a layer of this kind has and the registry each
+                comes from ({"mixer_norm": "norm", "mixer": "mixer", ...}); the
+                model builds exactly these from the `LayerSpec` and hands them to
+                `forward(ctx, hidden, layer, cache) -> hidden` as attributes of
+                `layer`. A block with other parts (four norms, one norm shared by two
+                branches) declares other roles; nothing outside its class changes.
 
 A part whose forward() looks at the step's host-side fields declares `graph_safe = False`.
 """
@@ -104,10 +113,20 @@ class Part:
     def tensor_specs(cls, spec: PartSpec) -> list[TensorSpec]:
         return []
 
+    @classmethod
+    def sub_parts(cls, spec: PartSpec) -> list[tuple[str, PartSpec]]:
+        """(registry name, PartSpec) of every part that this part builds inside itself."""
+        return []
+
     def __init__(self, spec: PartSpec, tensors: dict[str, torch.Tensor], runtime: Runtime) -> None:
         self.spec = spec
         self.runtime = runtime
         self.ops = runtime.ops
+
+    def build_sub_parts(self, tensors: dict[str, torch.Tensor]) -> list[Any]:
+        """The parts of `sub_parts`, built, in its order."""
+        return [REGISTRIES[registry].get(sub.kind)(sub, tensors, self.runtime)
+                for registry, sub in self.sub_parts(self.spec)]
 
     @classmethod
     def cache_need(cls, spec: PartSpec) -> CacheNeed | None:
@@ -139,6 +158,17 @@ class Registry:
         return sorted(self._classes)
 
 
+class Block:
+    """Arrangement of a layer's parts. `roles` maps each part's name in the layer to the
+    name of the registry it comes from."""
+
+    graph_safe = True
+    roles: dict[str, str] = {}
+
+    def forward(self, ctx, hidden, layer, cache):
+        raise NotImplementedError
+
+
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
@@ -146,3 +176,38 @@ POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
+
+REGISTRIES: dict[str, Registry] = {
+    "mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position_encoding": POSITION_ENCODINGS,
+    "block": BLOCKS, "embedding": EMBEDDINGS, "head": HEADS,
+}
+
+
+def layer_part_specs(layer) -> list[tuple[str, str, PartSpec]]:
+    """(role, registry name, PartSpec) for every part of a `LayerSpec`, in the order in which its
+    block kind declares them; raises when the layer lacks a declared role or has an undeclared one."""
+    block = BLOCKS.get(layer.block)
+    roles = getattr(block, "roles", None)
+    if not roles:
+        raise ValueError(f"block '{layer.block}' declares no roles (a dict: part name -> registry name)")
+    missing = [r for r in roles if r not in layer.parts]
+    extra = [r for r in layer.parts if r not in roles]
+    if missing or extra:
+        raise ValueError(
+            f"a '{layer.block}' layer has the parts {', '.join(roles)}; "
+            + (f"missing: {', '.join(missing)}; " if missing else "")
+            + (f"not declared by the block: {', '.join(extra)}" if extra else "")
+        )
+    for role, registry in roles.items():
+        if registry not in REGISTRIES:
+            raise ValueError(f"block '{layer.block}': role '{role}' names the registry '{registry}'; known: {', '.join(REGISTRIES)}")
+    return [(role, registry, layer.parts[role]) for role, registry in roles.items()]
+
+
+def with_sub_parts(registry: str, spec: PartSpec) -> list[tuple[str, PartSpec]]:
+    """(registry name, PartSpec) of a part and of every part nested inside it, outermost first."""
+    out = [(registry, spec)]
+    cls = REGISTRIES[registry].get(spec.kind)
+    for sub_registry, sub in getattr(cls, "sub_parts", lambda _spec: [])(spec):
+        out += with_sub_parts(sub_registry, sub)
+    return out

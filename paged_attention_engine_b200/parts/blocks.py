@@ -4,11 +4,13 @@ epilogue of each branch's last product."""
 
 from __future__ import annotations
 
-from .base import BLOCKS
+from .base import BLOCKS, Block
 
 
 @BLOCKS.register("pre_norm_residual")
-class PreNormResidual:
+class PreNormResidual(Block):
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
     def forward(self, ctx, hidden, layer, cache):
         # `hidden` may be a product that is still to be summed; the norm's kernel sums it, and
         # `materialized` then hands out the summed tensor without another launch.

@@ -24,35 +24,32 @@ from typing import Iterable
 import torch
 
 from ..config.model_spec import ModelSpec, PartSpec
-from ..parts.base import (
-    BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, TensorSpec,
-)
+from ..parts.base import REGISTRIES, TensorSpec, layer_part_specs, with_sub_parts
 
 
 class WeightsError(ValueError):
     """The checkpoint does not hold what the model reads; the message lists every fault."""
 
 
-def _part_specs(registry, spec: PartSpec) -> list[TensorSpec]:
-    return list(registry.get(spec.kind).tensor_specs(spec))
+def _part_specs(registry: str, spec: PartSpec) -> list[TensorSpec]:
+    """The tensors of a part and of the parts nested inside it."""
+    out: list[TensorSpec] = []
+    for sub_registry, sub in with_sub_parts(registry, spec):
+        out += list(REGISTRIES[sub_registry].get(sub.kind).tensor_specs(sub))
+    return out
 
 
 def collect_tensor_specs(spec: ModelSpec) -> dict[str, TensorSpec]:
     """Every tensor the model reads, by full name, in the order the parts name them."""
     found: list[TensorSpec] = []
-    found += _part_specs(EMBEDDINGS, spec.embedding)
+    found += _part_specs("embedding", spec.embedding)
     for layer in spec.layers:
-        BLOCKS.get(layer.block)  # an unknown arrangement fails here, before any file is opened
-        found += _part_specs(NORMS, layer.mixer_norm)
-        found += _part_specs(MIXERS, layer.mixer)
-        enc = layer.mixer.params.get("position_encoding")
-        if enc is not None:
-            enc_spec = PartSpec(enc["kind"], {k: v for k, v in enc.items() if k != "kind"}, layer.mixer.prefix)
-            found += _part_specs(POSITION_ENCODINGS, enc_spec)
-        found += _part_specs(NORMS, layer.feed_forward_norm)
-        found += _part_specs(FEED_FORWARDS, layer.feed_forward)
-    found += _part_specs(NORMS, spec.final_norm)
-    found += _part_specs(HEADS, spec.head)
+        # an unknown arrangement, or a layer without the parts its arrangement declares, fails
+        # here, before any file is opened
+        for _role, registry, part in layer_part_specs(layer):
+            found += _part_specs(registry, part)
+    found += _part_specs("norm", spec.final_norm)
+    found += _part_specs("head", spec.head)
     out: dict[str, TensorSpec] = {}
     for t in found:
         if t.name in out and out[t.name].shape != t.shape:

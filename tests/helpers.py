@@ -67,6 +67,14 @@ TINY_D = dict(
 TINY = {"tiny_a": (TINY_A, 4, 0), "tiny_b": (TINY_B, 16, 1), "tiny_c": (TINY_C, 8, 2), "tiny_d": (TINY_D, 16, 3)}  # config, page size, seed
 
 
+def decoder_layer(mixer_norm, mixer, feed_forward_norm, feed_forward):
+    """A `LayerSpec` of the usual arrangement: norm, mixer, add; norm, feed-forward, add."""
+    from paged_attention_engine_b200.config import LayerSpec
+
+    return LayerSpec("pre_norm_residual", dict(
+        mixer_norm=mixer_norm, mixer=mixer, feed_forward_norm=feed_forward_norm, feed_forward=feed_forward))
+
+
 def write_model(folder: Path, raw: dict, seed: int, dtype: torch.dtype, sharpen: float = 1.0) -> Path:
     """A random model folder; `sharpen` scales every q and k projection so that attention
     scores spread out and one wrong, missing or extra key changes the logits visibly."""

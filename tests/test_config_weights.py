@@ -146,3 +146,78 @@ def test_missing_files_are_named(tmp_path):
     with pytest.raises(WeightsError) as err:
         load_tensors(tmp_path, spec, torch.float32, "cpu")
     assert "model.safetensors" in str(err.value)
+
+
+def _split_into_shards(folder):
+    """Rewrites a one-file checkpoint as two shards and an index, as larger checkpoints come."""
+    path = folder / "model.safetensors"
+    stored = load_file(str(path))
+    names = sorted(stored)
+    first, second = names[: len(names) // 2], names[len(names) // 2 :]
+    save_file({n: stored[n] for n in first}, str(folder / "model-00001-of-00002.safetensors"))
+    save_file({n: stored[n] for n in second}, str(folder / "model-00002-of-00002.safetensors"))
+    weight_map = {n: "model-00001-of-00002.safetensors" for n in first}
+    weight_map.update({n: "model-00002-of-00002.safetensors" for n in second})
+    (folder / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    path.unlink()
+    return stored
+
+
+def test_loader_reads_shards_through_the_index(tmp_path):
+    folder = write_random_model(tmp_path / "m", helpers.TINY_B, seed=4, dtype=torch.float32)
+    _, spec = resolve_folder(folder)
+    whole = load_tensors(folder, spec, torch.float32, "cpu")
+    stored = _split_into_shards(folder)
+    sharded = load_tensors(folder, spec, torch.float32, "cpu")
+    assert set(sharded) == set(whole) == set(stored)
+    for name in whole:
+        assert torch.equal(sharded[name], whole[name]), name
+
+
+def test_a_shard_that_the_index_names_but_is_not_there(tmp_path):
+    folder = write_random_model(tmp_path / "m", helpers.TINY_B, seed=4, dtype=torch.float32)
+    _, spec = resolve_folder(folder)
+    _split_into_shards(folder)
+    (folder / "model-00002-of-00002.safetensors").unlink()
+    with pytest.raises(WeightsError) as err:
+        load_tensors(folder, spec, torch.float32, "cpu")
+    assert "model-00002-of-00002.safetensors" in str(err.value) and "not there" in str(err.value)
+
+
+def test_a_shard_without_a_tensor_lists_it_as_missing(tmp_path):
+    folder = write_random_model(tmp_path / "m", helpers.TINY_B, seed=4, dtype=torch.float32)
+    _, spec = resolve_folder(folder)
+    _split_into_shards(folder)
+    shard = str(folder / "model-00001-of-00002.safetensors")
+    stored = load_file(shard)
+    gone = sorted(stored)[0]
+    del stored[gone]
+    save_file(stored, shard)
+    with pytest.raises(WeightsError) as err:
+        load_tensors(folder, spec, torch.float32, "cpu")
+    assert "missing (1)" in str(err.value) and gone in str(err.value)
+
+
+def test_engine_options_size_the_pool_by_pages_or_by_bytes():
+    from paged_attention_engine_b200.cache import plan_cache
+    from paged_attention_engine_b200.config import EngineConfig
+
+    assert EngineConfig().pool_blocks(1000) == 3584                       # the reference's pool
+    assert EngineConfig(num_blocks=77).pool_blocks(1000) == 77
+    _, spec = resolve(dict(helpers.TINY_B))
+    plan = plan_cache(spec)
+    # tiny B: 3 layers x 1 kv head x 32 x (keys + values) x 16 tokens x 4 bytes
+    per_block = plan.bytes_per_block(16, 4)
+    assert per_block == 3 * 1 * 32 * 2 * 16 * 4
+    assert EngineConfig(kv_bytes=10 * per_block + per_block - 1).pool_blocks(per_block) == 10
+    # tiny C has two page groups (windowed and not), each with a pool of its own
+    _, spec_c = resolve(dict(helpers.TINY_C))
+    assert plan_cache(spec_c).bytes_per_block(8, 2) == 4 * 5 * 48 * 2 * 8 * 2
+    for bad in (dict(num_blocks=4, kv_bytes=4096), dict(block_size=0), dict(kv_bytes=0), dict(max_num_seqs=0),
+                dict(dtype="float16"), dict(admission_margin_blocks=-1)):
+        with pytest.raises(ConfigError):
+            EngineConfig(**bad)
+    with pytest.raises(ConfigError, match="does not pay for one page"):
+        EngineConfig(kv_bytes=per_block - 1).pool_blocks(per_block)
+    with pytest.raises(ConfigError, match="unknown engine option"):
+        EngineConfig.from_options({"num_block": 3})

@@ -112,7 +112,7 @@ def test_attention_part_alone(runtime_of, dtype, window):
     """The mixer over its own little cache: two portions and single tokens of one request
     against plain whole-sequence attention."""
     from paged_attention_engine_b200.cache import CacheManager, PagedKVCache, plan_cache
-    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from paged_attention_engine_b200.config import ModelSpec, PartSpec, ScheduleEntry
     from paged_attention_engine_b200.engine.batch import BatchBuilder, StepEntry
     from paged_attention_engine_b200.parts import MIXERS
 
@@ -122,7 +122,7 @@ def test_attention_part_alone(runtime_of, dtype, window):
     mixer_spec = PartSpec("gqa_attention", params, "a")
     norm = PartSpec("rms_norm", {"size": hidden, "eps": 1e-6}, "n")
     spec = ModelSpec("test", 8, hidden, 512, PartSpec("token_embedding", {"vocab_size": 8, "hidden_size": hidden}, "e"),
-                     (LayerSpec("pre_norm_residual", norm, mixer_spec, norm, PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 8}, "f")),),
+                     (helpers.decoder_layer(norm, mixer_spec, norm, PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 8}, "f")),),
                      (ScheduleEntry(0),), norm, PartSpec("lm_head", {"vocab_size": 8, "hidden_size": hidden, "tied_to": "e.weight"}, "h"))
     gen = torch.Generator().manual_seed(5)
     w = {}

@@ -14,6 +14,10 @@ a change to any file of the package.
     factor, for a chosen part of the frequencies only (the rest are not rotated). The
     package's attention part uses it through the same `table(ctx)` as its own.
 
+  * `sandwich_norm` is another arrangement of a layer: a norm before AND after each branch
+    (four norms, with roles of its own names). The block kind declares its parts; the
+    loader, the random weights, the cache plan and the model follow that declaration.
+
 These are toys for the test, not models of anything.
 """
 
@@ -113,7 +117,7 @@ def _register_toys():
 
 
 def _spec(hidden, vocab, schedule_kind):
-    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from paged_attention_engine_b200.config import ModelSpec, PartSpec, ScheduleEntry
 
     def norm(prefix):
         return PartSpec("rms_norm", {"size": hidden, "eps": 1e-5}, prefix)
@@ -122,9 +126,9 @@ def _spec(hidden, vocab, schedule_kind):
         "hidden_size": hidden, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qkv_bias": True, "scale": 0.25,
         "window": 0, "position_encoding": {"kind": "rotary", "head_dim": 16, "theta": 1e4}}, "l0.attn")
     layers = (
-        LayerSpec("pre_norm_residual", norm("l0.n1"), attention, norm("l0.n2"),
+        helpers.decoder_layer(norm("l0.n1"), attention, norm("l0.n2"),
                   PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48}, "l0.ff")),
-        LayerSpec("pre_norm_residual", norm("l1.n1"), PartSpec("running_mean", {"hidden_size": hidden}), norm("l1.n2"),
+        helpers.decoder_layer(norm("l1.n1"), PartSpec("running_mean", {"hidden_size": hidden}), norm("l1.n2"),
                   PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 40}, "l1.ff")),
     )
     schedule = {
@@ -209,7 +213,7 @@ def test_toy_model_is_registered_built_and_stepped(schedule_kind):
 
 
 def _routed_spec(hidden, vocab):
-    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from paged_attention_engine_b200.config import ModelSpec, PartSpec, ScheduleEntry
 
     def norm(prefix):
         return PartSpec("rms_norm", {"size": hidden, "eps": 1e-5}, prefix)
@@ -221,9 +225,9 @@ def _routed_spec(hidden, vocab):
             prefix)
 
     layers = (
-        LayerSpec("pre_norm_residual", norm("l0.n1"), attention("l0.attn"), norm("l0.n2"),
+        helpers.decoder_layer(norm("l0.n1"), attention("l0.attn"), norm("l0.n2"),
                   PartSpec("top1_experts", {"hidden_size": hidden, "intermediate_size": 24, "experts": 3}, "l0.ff")),
-        LayerSpec("pre_norm_residual", norm("l1.n1"), attention("l1.attn"), norm("l1.n2"),
+        helpers.decoder_layer(norm("l1.n1"), attention("l1.attn"), norm("l1.n2"),
                   PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48}, "l1.ff")),
     )
     return ModelSpec("toy_routed", vocab, hidden, 256, PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden}, "emb"),
@@ -308,4 +312,111 @@ def test_routed_feed_forward_and_another_position_encoding():
         gap = (got[key] - want).abs().max().item()
         assert gap <= helpers.tolerance(torch.float32, want), f"{key}: {gap}"
     assert used == {0, 1, 2}, "every expert got tokens"
+    assert cache.manager.allocators[0].num_free == 24
+
+
+def _register_sandwich():
+    from paged_attention_engine_b200.parts import BLOCKS, Block
+
+    if "sandwich_norm" in BLOCKS.names():
+        return
+
+    @BLOCKS.register("sandwich_norm")
+    class SandwichNorm(Block):
+        """x += after_mixer(mixer(before_mixer(x))); x += after_ff(ff(before_ff(x)))."""
+
+        roles = {"before_mixer": "norm", "token_mixer": "mixer", "after_mixer": "norm",
+                 "before_ff": "norm", "ff": "feed_forward", "after_ff": "norm"}
+
+        def forward(self, ctx, hidden, layer, cache):
+            ops = ctx.ops
+            hidden = ops.materialized(hidden)
+            zero = torch.zeros_like(hidden)
+            branch = layer.token_mixer.forward(ctx, layer.before_mixer.forward(ctx, hidden), zero, cache)
+            hidden = hidden + ops.materialized(layer.after_mixer.forward(ctx, branch))
+            branch = layer.ff.forward(ctx, layer.before_ff.forward(ctx, hidden), zero)
+            return hidden + ops.materialized(layer.after_ff.forward(ctx, branch))
+
+
+def test_a_block_kind_declares_its_own_parts():
+    """A layer with four norms under role names that no file of the package knows: the tensors
+    of all six parts are found by the loader's walk, pages go to the role that needs them, and the
+    model steps in portions and single tokens like any other."""
+    from paged_attention_engine_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.kernels import ops
+    from paged_attention_engine_b200.parts import Runtime
+    from paged_attention_engine_b200.weights import collect_tensor_specs, place_tensors
+    from paged_attention_engine_b200.weights.random_init import draw
+    from plain import qwen2_plain as plain
+
+    _register_sandwich()
+    hidden, vocab, eps = 48, 71, 1e-5
+
+    def norm(prefix):
+        return PartSpec("rms_norm", {"size": hidden, "eps": eps}, prefix)
+
+    def layer(p, inner):
+        return LayerSpec("sandwich_norm", {
+            "before_mixer": norm(p + "n1"), "after_mixer": norm(p + "n2"), "before_ff": norm(p + "n3"), "after_ff": norm(p + "n4"),
+            "token_mixer": PartSpec("gqa_attention", {
+                "hidden_size": hidden, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "qkv_bias": True, "scale": 0.25,
+                "window": 0, "position_encoding": {"kind": "rotary", "head_dim": 16, "theta": 1e4}}, p + "attn"),
+            "ff": PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": inner}, p + "ff"),
+        })
+
+    spec = ModelSpec("toy_sandwich", vocab, hidden, 256, PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden}, "emb"),
+                     (layer("l0.", 32), layer("l1.", 40)), (ScheduleEntry(0), ScheduleEntry(1)), norm("final"),
+                     PartSpec("lm_head", {"vocab_size": vocab, "hidden_size": hidden, "tied_to": "emb.weight"}, "head"))
+    names = collect_tensor_specs(spec)
+    assert {"l0.n1.weight", "l0.n4.weight", "l1.n3.weight", "l1.attn.q_proj.bias", "l0.ff.down_proj.weight"} <= set(names)
+    with pytest.raises(ValueError, match="missing: after_ff"):
+        collect_tensor_specs(ModelSpec(
+            "broken", vocab, hidden, 256, spec.embedding,
+            (LayerSpec("sandwich_norm", {k: v for k, v in spec.layers[0].parts.items() if k != "after_ff"}),),
+            (ScheduleEntry(0),), spec.final_norm, spec.head))
+
+    gen = torch.Generator().manual_seed(29)
+    raw = {name: draw(t, gen) * (5.0 if ".q_proj." in name or ".k_proj." in name else 1.0) for name, t in sorted(names.items())}
+    runtime = Runtime(ops, torch.float32, torch.device("cuda:0"))
+    engine = Engine(None, spec, place_tensors(dict(raw), spec, torch.float32, runtime.device), runtime)
+    assert len(engine.cache_plan.groups) == 1 and engine.cache_plan.groups[0].entries == (0, 1)
+    cache = engine.new_paged_cache(num_blocks=24, block_size=8, max_num_seqs=3)
+    runner = engine.new_runner(cache)
+    requests = {"a": helpers.random_tokens(vocab, 33, 11), "b": helpers.random_tokens(vocab, 21, 12), "c": helpers.random_tokens(vocab, 27, 13)}
+    trace = helpers.trace_mixed(requests, seed=6, live_limit=2, decode_tail=5)
+    outputs = {}
+    for record in trace:
+        entries = []
+        for item in record["entries"]:
+            if not cache.manager.is_live(item["id"]):
+                assert runner.begin_request(item["id"])
+            assert cache.manager.reserve(item["id"], len(item["tokens"])).ok
+            entries.append(StepEntry(item["id"], item["tokens"], item["want"]))
+        outputs[record["step"]] = runner.step(entries).logits.float().cpu()
+        for key in record["end"]:
+            runner.end_request(key)
+    got = helpers.collect(trace, outputs, requests)
+
+    def whole(ids):
+        x = raw["emb.weight"][torch.tensor(ids)]
+        n = len(ids)
+        cos, sin = plain.rotary_tables(plain.rotary_inv_freq(16, 1e4), torch.arange(n), torch.float32)
+        for p in ("l0.", "l1."):
+            y = plain.rms_norm(x, raw[p + "n1.weight"], eps)
+            q = plain.apply_rotary(plain.linear(y, raw[p + "attn.q_proj.weight"], raw[p + "attn.q_proj.bias"]).view(n, 3, 16), cos, sin)
+            k = plain.apply_rotary(plain.linear(y, raw[p + "attn.k_proj.weight"], raw[p + "attn.k_proj.bias"]).view(n, 1, 16), cos, sin)
+            v = plain.linear(y, raw[p + "attn.v_proj.weight"], raw[p + "attn.v_proj.bias"]).view(n, 1, 16)
+            branch = plain.linear(plain.attention(q, k, v, 0.25).reshape(n, 48), raw[p + "attn.o_proj.weight"])
+            x = x + plain.rms_norm(branch, raw[p + "n2.weight"], eps)
+            y = plain.rms_norm(x, raw[p + "n3.weight"], eps)
+            branch = plain.swiglu(y, raw[p + "ff.gate_proj.weight"], raw[p + "ff.up_proj.weight"], raw[p + "ff.down_proj.weight"])
+            x = x + plain.rms_norm(branch, raw[p + "n4.weight"], eps)
+        return plain.linear(plain.rms_norm(x, raw["final.weight"], eps), raw["emb.weight"])
+
+    for key, ids in requests.items():
+        want = whole(ids)
+        gap = (got[key] - want).abs().max().item()
+        assert gap <= helpers.tolerance(torch.float32, want), f"{key}: {gap}"
     assert cache.manager.allocators[0].num_free == 24
