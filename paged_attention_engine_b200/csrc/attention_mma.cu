@@ -46,8 +46,7 @@ PAE_EXPORT long long pae_decode_scratch_floats(int seqs, int heads, int d, int m
 // Requests that bring exactly one token: out[token, head, :] over keys [0, kv_len) (or the
 // last `window`). Requests with more tokens are skipped. `scratch` holds
 // pae_decode_scratch_floats(...) floats; `slice_keys` is a multiple of 16 and
-// max_slices * slice_keys covers the longest request. With a null `scratch` and at most 32
-// slices the slices are merged on chip by a thread-block cluster instead.
+// max_slices * slice_keys covers the longest request.
 PAE_EXPORT int pae_paged_attention_decode(void* out, const void* qkv, const void* keys, const void* values,
                                           const int* block_table, int table_width, const int* q_start,
                                           const int* kv_len, int seqs, int heads, int kv_heads, int d, int page_size,

@@ -27,11 +27,11 @@
 
 #include "common.cuh"
 
-#include <cooperative_groups.h>
 
 #include <cfloat>
 #include <mutex>
-#include <unordered_set>
+#include <set>
+#include <utility>
 
 namespace pae_attention {
 
@@ -39,7 +39,6 @@ using namespace pae;
 
 
 constexpr int TILE_KEYS = 16;            // keys per MMA step of the decode kernel: never straddles a page
-constexpr int DECODE_WARPS = 4;         // warps (slices) per block of the cluster form
 // The sliced decode kernel: warps (slices) per block, and tiles of 16 keys that a warp keeps in
 // flight. A tile takes about a microsecond to arrive and a slice is a handful of tiles, so a
 // slice's time is its number of tiles divided by the depth, in microseconds. Measured at the
@@ -349,133 +348,6 @@ __global__ void __launch_bounds__(SLICE_WARPS * 32) decode_slices_kernel(const D
   }
 }
 
-// ---------------------------------------------------------------------------------------
-// decode, merged on chip: the blocks that hold the slices of one (request, kv head) form a
-// thread-block cluster; every warp leaves its slice's unnormalised output, maximum and sum in
-// its block's shared memory, and after a cluster barrier block r of the cluster merges query
-// head r of the group by reading the others' shared memory (distributed shared memory). No
-// scratch in global memory and no second kernel. At most 8 blocks x 4 warps = 32 slices.
-// ---------------------------------------------------------------------------------------
-constexpr int CLUSTER_MAX_SLICES = 32;
-
-template <int D>
-__global__ void __launch_bounds__(DECODE_WARPS * 32) decode_cluster_kernel(const DecodeParams p, __nv_bfloat16* out) {
-  namespace cg = cooperative_groups;
-  cg::cluster_group cluster = cg::this_cluster();
-  dependent_launch_trigger();
-  extern __shared__ __align__(128) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int slice = blockIdx.x * DECODE_WARPS + warp;
-  const int g = blockIdx.y, b = blockIdx.z;
-  const int token = p.q_start[b];
-  const bool single = p.q_start[b + 1] - token == 1;          // the same for every block of the cluster
-  const int kv_len = p.kv_len[b];
-  const int first_key = p.window > 0 ? max(0, kv_len - p.window) : 0;
-  const int base = (first_key / TILE_KEYS) * TILE_KEYS;
-  const int begin = base + slice * p.slice_keys;
-  const int end = min(kv_len, begin + p.slice_keys);
-  const bool mine = single && slice < p.max_slices && begin < kv_len;
-  const int groups = p.heads / p.kv_heads;
-  const int row_elems = (p.heads + 2 * p.kv_heads) * D;
-  constexpr int TILE_BYTES = TILE_KEYS * D * 2;
-  uint8_t* staging = smem + warp * 4 * TILE_BYTES;            // two stages of (K tile, V tile)
-  const uint32_t staging_u32 = smem_u32(staging);
-  // Behind the staging: per warp [16 heads][D] floats of output, 16 maxima, 16 sums.
-  float* partial = (float*)(smem + DECODE_WARPS * 4 * TILE_BYTES) + warp * (16 * D + 32);
-  const int* table = p.block_table + (size_t)b * p.table_width;
-
-  auto fetch = [&](int stage, int key0) {
-    const int page = table[key0 / p.page_size];
-    const size_t row0 = ((size_t)page * p.kv_heads + g) * p.page_size + (key0 % p.page_size);
-    const uint32_t k_dst = staging_u32 + stage * 2 * TILE_BYTES;
-    constexpr int CHUNKS = TILE_KEYS * D / 8;
-#pragma unroll
-    for (int i = lane; i < CHUNKS; i += 32) {
-      const int row = i / (D / 8), c = i % (D / 8);
-      const int off = TileLayout<D>::offset_bytes(row, c);
-      cp_async16(k_dst + off, p.keys + (row0 + row) * D + c * 8);
-      cp_async16(k_dst + TILE_BYTES + off, p.values + (row0 + row) * D + c * 8);
-    }
-  };
-
-  const bool early = mine && begin + TILE_KEYS <= kv_len - 1;   // the first tile holds earlier tokens only
-  if (early) fetch(0, begin);
-  dependent_launch_wait();
-  if (mine) {
-    uint32_t q[D / 16][4];
-    load_query_fragments<D>(q, [&](int r) -> const __nv_bfloat16* {
-      return r < groups ? p.qkv + (size_t)token * row_elems + (size_t)(g * groups + r) * D : nullptr;
-    });
-    if (!early) fetch(0, begin);
-    cp_async_commit();
-    float o[D / 8][4];
-#pragma unroll
-    for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-    float row_max[2] = {-FLT_MAX, -FLT_MAX}, row_sum[2] = {0.f, 0.f};
-    const int tiles = (end - begin + TILE_KEYS - 1) / TILE_KEYS;
-    for (int t = 0; t < tiles; ++t) {
-      if (t + 1 < tiles) fetch((t + 1) & 1, begin + (t + 1) * TILE_KEYS);
-      cp_async_commit();
-      cp_async_wait<1>();
-      __syncwarp();
-      const uint32_t k_tile = staging_u32 + (t & 1) * 2 * TILE_BYTES;
-      const int key0 = begin + t * TILE_KEYS;
-      float s[2][4];
-      scores_16_keys<D>(s, q, k_tile, 0);
-      uint32_t pa[4];
-      softmax_step<D>(s, row_max, row_sum, o, pa, p.scale_log2, key0 >= first_key && key0 + TILE_KEYS <= end,
-                      [&](int, int key) { return key0 + key >= first_key && key0 + key < end; });
-      accumulate_16_keys<D>(o, pa, k_tile + TILE_BYTES, 0);
-      __syncwarp();
-    }
-    cp_async_wait<0>();
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = (lane >> 2) + half * 8;
-      if (r >= groups) continue;
-#pragma unroll
-      for (int n = 0; n < D / 8; ++n)
-        *(float2*)(partial + r * D + n * 8 + (lane & 3) * 2) = make_float2(o[n][half * 2], o[n][half * 2 + 1]);
-      if ((lane & 3) == 0) {
-        partial[16 * D + r] = row_max[half];
-        partial[16 * D + 16 + r] = row_sum[half];
-      }
-    }
-  }
-  cluster.sync();            // every slice of this (request, kv head) lies in some block's shared memory
-
-  const int rank = (int)cluster.block_rank();
-  const int blocks = (int)cluster.num_blocks();
-  if (single) {
-    const int slices = min(p.max_slices, (kv_len - base + p.slice_keys - 1) / p.slice_keys);
-    float* mine_base = (float*)(smem + DECODE_WARPS * 4 * TILE_BYTES);
-    // Block `rank` merges heads rank, rank + blocks, ... of the group; thread d owns dimension d.
-    for (int r = rank; r < groups; r += blocks) {
-      float top = -FLT_MAX;
-      for (int s = 0; s < slices; ++s) {
-        const float* remote = cluster.map_shared_rank(mine_base, s / DECODE_WARPS) + (s % DECODE_WARPS) * (16 * D + 32);
-        top = fmaxf(top, remote[16 * D + r]);
-      }
-      float total = 0.f;
-      for (int s = 0; s < slices; ++s) {
-        const float* remote = cluster.map_shared_rank(mine_base, s / DECODE_WARPS) + (s % DECODE_WARPS) * (16 * D + 32);
-        total += remote[16 * D + 16 + r] * exp2f(remote[16 * D + r] - top);
-      }
-      const float inv = total > 0.f ? 1.f / total : 0.f;
-      for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float v = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < slices; ++s) {
-          const float* remote = cluster.map_shared_rank(mine_base, s / DECODE_WARPS) + (s % DECODE_WARPS) * (16 * D + 32);
-          v += remote[r * D + d] * exp2f(remote[16 * D + r] - top);
-        }
-        out[((size_t)token * p.heads + g * groups + r) * D + d] = __float2bfloat16_rn(v * inv);
-      }
-    }
-  }
-  cluster.sync();            // nobody leaves while its shared memory may still be read
-}
-
 // out[token, head, :] = sum_s w_s part_out[s] / sum_s w_s part_sum[s], w_s = 2^(max_s - max).
 // One block of four warps per (request, head). Everything the block needs is asked for before
 // anything is waited for: a thread's slice maxima and sums, and the partial outputs of the
@@ -730,17 +602,22 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
   }  // the block's two tiles
 }
 
-// Raises a kernel's dynamic shared memory limit, once per kernel and process.
+// Raises a kernel's dynamic shared memory limit, once per kernel and device (the attribute
+// belongs to the kernel as loaded on one device).
 template <typename Kernel>
 int allow_smem(Kernel kernel, size_t bytes, const char* what) {
   static std::mutex mutex;
-  static std::unordered_set<const void*> done;
+  static std::set<std::pair<int, const void*>> done;
   if (bytes <= 48 * 1024) return 0;
+  int device = -1;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return fail(100, "%s: cudaGetDevice: %s", what, cudaGetErrorString(err));
   std::lock_guard<std::mutex> guard(mutex);
-  if (done.count((const void*)kernel)) return 0;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  const std::pair<int, const void*> key(device, (const void*)kernel);
+  if (done.count(key)) return 0;
+  err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (err != cudaSuccess) return fail(100, "%s: %s", what, cudaGetErrorString(err));
-  done.insert((const void*)kernel);
+  done.insert(key);
   return 0;
 }
 
@@ -753,21 +630,9 @@ int launch_decode(const DecodeParams& p, __nv_bfloat16* out, int seqs, cudaStrea
   dim3 grid((p.max_slices + SLICE_WARPS - 1) / SLICE_WARPS, p.kv_heads, seqs);
   launch_kernel(decode_slices_kernel<D>, grid, SLICE_WARPS * 32, bytes, s, p);
   if (int err = check_launch("paged_attention_decode")) return err;
-  if ((size_t)(p.max_slices + 4 * D) * sizeof(float) > 40 * 1024) return fail(2, "paged_attention_decode: %d slices are more than the merge takes", p.max_slices);
   launch_kernel(merge_slices_kernel<D>, dim3(p.heads, seqs), MERGE_WARPS * 32, (p.max_slices + MERGE_WARPS * D) * sizeof(float), s, out, p.part_out, p.part_max, p.part_sum, p.q_start,
                                                                      p.kv_len, p.heads, p.window, p.slice_keys, p.max_slices);
   return check_launch("paged_attention_merge");
-}
-
-// The cluster form: one cluster of ceil(max_slices / 4) <= 8 blocks per (request, kv head).
-template <int D>
-int launch_decode_cluster(const DecodeParams& p, __nv_bfloat16* out, int seqs, cudaStream_t s) {
-  const size_t bytes = (size_t)DECODE_WARPS * 4 * TILE_KEYS * D * 2 + (size_t)DECODE_WARPS * (16 * D + 32) * sizeof(float);
-  if (int err = allow_smem(decode_cluster_kernel<D>, bytes, "paged_attention_decode")) return err;
-  const unsigned blocks = (unsigned)((p.max_slices + DECODE_WARPS - 1) / DECODE_WARPS);
-  dim3 grid(blocks, p.kv_heads, seqs);
-  launch_kernel_cluster(decode_cluster_kernel<D>, grid, DECODE_WARPS * 32, bytes, s, blocks, p, out);
-  return check_launch("paged_attention_decode");
 }
 
 template <int D>
@@ -798,6 +663,11 @@ inline int decode_with_scratch(void* out, const void* qkv, const void* keys, con
   if (int err = check_sizes("paged_attention_decode", heads, kv_heads, d, page_size, seqs)) return err;
   if (heads / kv_heads > 16) return fail(2, "paged_attention_decode: %d query heads per kv head are more than 16", heads / kv_heads);
   if (slice_keys < 16 || slice_keys % 16 || max_slices < 1) return fail(2, "paged_attention_decode: slices of %d keys x %d", slice_keys, max_slices);
+  if (scratch == nullptr) return fail(2, "paged_attention_decode: no scratch for the slices' partial results was given");
+  // The merge keeps a weight per slice (and a row per warp) in shared memory: refused here, before anything is launched.
+  if ((size_t)(max_slices + MERGE_WARPS * d) * sizeof(float) > 40 * 1024)
+    return fail(2, "paged_attention_decode: %d slices are more than the merge takes (%d at head size %d)", max_slices,
+                (int)(40 * 1024 / sizeof(float)) - MERGE_WARPS * d, d);
   DecodeParams p{};
   p.qkv = (const __nv_bfloat16*)qkv;
   p.keys = (const __nv_bfloat16*)keys;
@@ -817,12 +687,6 @@ inline int decode_with_scratch(void* out, const void* qkv, const void* keys, con
   p.slice_keys = slice_keys;
   p.max_slices = max_slices;
   p.scale_log2 = scale * LOG2E;
-  if (scratch == nullptr) {
-    if (max_slices > CLUSTER_MAX_SLICES) return fail(2, "paged_attention_decode: %d slices are more than a cluster's %d", max_slices, CLUSTER_MAX_SLICES);
-    if (d == 32) return launch_decode_cluster<32>(p, (__nv_bfloat16*)out, seqs, s);
-    if (d == 64) return launch_decode_cluster<64>(p, (__nv_bfloat16*)out, seqs, s);
-    return launch_decode_cluster<128>(p, (__nv_bfloat16*)out, seqs, s);
-  }
   if (d == 32) return launch_decode<32>(p, (__nv_bfloat16*)out, seqs, s);
   if (d == 64) return launch_decode<64>(p, (__nv_bfloat16*)out, seqs, s);
   return launch_decode<128>(p, (__nv_bfloat16*)out, seqs, s);

@@ -751,9 +751,14 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
   // the tile covers): the first tile's table entries, before the wait.
   const int box_rows = min(p.page_size, BKEYS);
   const int last_page = active ? (kv_end - 1) / p.page_size : 0;     // the last page that holds a visible key
+  // The first tile starts on a multiple of 64 keys, which may lie pages before the window's first
+  // key; those pages may have been given back (their table entries are holes). Their keys are
+  // masked, so the window's first page stands in for them.
+  const int window_page = first_key / p.page_size;
   int first_page = 0;
   if (warp == 0 && active && lane < BKEYS / box_rows)
-    first_page = p.block_table[(size_t)b * p.table_width + min((kv_begin + lane * box_rows) / p.page_size, last_page)];
+    first_page = p.block_table[(size_t)b * p.table_width +
+                               max(min((kv_begin + lane * box_rows) / p.page_size, last_page), window_page)];
   dependent_launch_wait();
 
   if (warp == 0) {
@@ -777,7 +782,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
       // the request will do; the last visible one is taken.
       auto box_row = [&](int t) {
         const int key = kv_begin + t * BKEYS + lane * box_rows;
-        const int page = table[min(key / p.page_size, last_page)];
+        const int page = table[max(min(key / p.page_size, last_page), window_page)];
         return (page * p.kv_heads + g) * p.page_size + key % p.page_size;
       };
       int row = mine ? (first_page * p.kv_heads + g) * p.page_size + (kv_begin + lane * box_rows) % p.page_size : 0;
@@ -1039,8 +1044,6 @@ int sm_count() {
   return count;
 }
 
-int last_cluster_blocks = 0;     // of the last launch: 0 for the paired kernel, else blocks per query tile
-
 // form 0 picks by the size of the launch: the paired kernel when it has at least two blocks per
 // SM; else the wide one, and when its blocks are fewer than half of the SMs (a short portion
 // of a prompt over a long context) a query tile's keys are shared out over a cluster of 2, 4 or
@@ -1050,7 +1053,7 @@ int last_cluster_blocks = 0;     // of the last launch: 0 for the paired kernel,
 // 1: wide, no clusters; 2: paired; 4, 8, 16: wide in clusters of 2, 4, 8.
 template <int D>
 int launch(const Params& p, const void* qkv, const void* keys, const void* values, int tokens, long long pages, int seqs,
-           int working_seqs, int max_q_len, int max_kv_len, int form, cudaStream_t stream) {
+           int working_seqs, int max_q_len, int max_kv_len, int form, int* chosen, cudaStream_t stream) {
   dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
   // Blocks of requests that this launch leaves to the decode kernel return at once: they do not count.
   const long long blocks = (long long)grid.x * grid.y * working_seqs;
@@ -1080,7 +1083,7 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
     if (err != cudaSuccess) return fail(100, "paged_attention_tcgen05: %s", cudaGetErrorString(err));
     configured = true;
   }
-  last_cluster_blocks = use_paired ? 0 : (int)ranks;
+  if (chosen != nullptr) *chosen = use_paired ? 0 : (int)ranks;
   if (use_paired) {
     launch_kernel(paired::prefill_tcgen05_paired_kernel<D>, grid, paired::THREADS, paired::Layout<D>::SMEM_BYTES, stream, map_q, map_k,
                   map_v, p);
@@ -1096,22 +1099,19 @@ int launch(const Params& p, const void* qkv, const void* keys, const void* value
 
 }  // namespace
 
-// Blocks per query tile in the last launch (1: no clusters; 0: the paired kernel). For tests.
-PAE_EXPORT int pae_attention_tcgen05_last_cluster() { return last_cluster_blocks; }
-
 PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, int page_size) {
   return (d == 64 || d == 128) && (page_size == 16 || page_size == 32 || page_size == 64 || page_size == 128) &&
          kv_heads >= 1 && heads % kv_heads == 0;
 }
 
 // Attention of every request that brings more than one token (or every request, unless
-// skip_single; `singles` is how many bring one, -1 when the caller does not know). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests). qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
+// skip_single; `singles` is how many bring one, -1 when the caller does not know). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests); `chosen` (a host pointer, or null) receives the blocks per query tile of this launch: 1 without clusters, 0 for the paired kernel. qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
 PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, const void* keys, const void* values,
                                                    long long pages, const int* block_table, int table_width,
                                                    const int* q_start, const int* q_pos0, const int* kv_len, int tokens,
                                                    int seqs, int max_q_len, int max_kv_len, int heads, int kv_heads, int d,
-                                                   int page_size, float scale, int window, int skip_single, int singles, int form, int* error,
-                                                   void* stream) {
+                                                   int page_size, float scale, int window, int skip_single, int singles, int form, int* chosen,
+                                                   int* error, void* stream) {
   if (seqs == 0 || max_q_len == 0 || tokens == 0) return 0;
   if (!pae_attention_tcgen05_supports(heads, kv_heads, d, page_size))
     return fail(2, "paged_attention_tcgen05: head_dim %d with pages of %d is not taken (64 or 128; 16, 32, 64 or 128)", d, page_size);
@@ -1134,8 +1134,8 @@ PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, c
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
   const int working_seqs = skip_single && singles > 0 && singles < seqs ? seqs - singles : seqs;
-  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, s);
-  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, s);
+  if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, chosen, s);
+  return launch<128>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, chosen, s);
 }
 
 PAE_DEFINE_LAST_ERROR()

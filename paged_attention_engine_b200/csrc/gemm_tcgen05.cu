@@ -65,6 +65,7 @@ struct Params {
   __nv_bfloat16* values;
   int heads, kv_heads, head_dim, page_size;
   int* error;
+  int skip_kb;       // self-test of the give-up path only: the k-block (of each block's range) that is never loaded
 };
 
 // ---------------------------------------------------------------------------------------
@@ -97,8 +98,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Waits for a phase of an mbarrier, at most WAIT_LIMIT polls. On giving up it raises the
 // block's abort flag and records `code`; it also returns false as soon as another role
 // has raised the flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* error, int code,
+                                          uint32_t limit = WAIT_LIMIT) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (i > 64) __nanosleep(64);
@@ -360,10 +362,18 @@ struct Tile {
   static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
-template <int BN, int MODE>
+// SELFTEST is the kernel with which a test makes a wait run out, to see the give-up path work:
+// the producer never loads k-block `p.skip_kb` (nothing is in flight for it, its barrier is
+// never armed), so the MMA issuer's wait for that stage reaches its limit (a short one here),
+// raises the abort flag and the error word, and every role leaves through the same code as in
+// the product: loads in flight are waited for, tensor memory is freed, the block returns.
+constexpr uint32_t SELFTEST_WAIT_LIMIT = 1u << 12;
+
+template <int BN, int MODE, bool SELFTEST = false>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_b, const Params p) {
   using T = Tile<BN>;
+  constexpr uint32_t limit = SELFTEST ? SELFTEST_WAIT_LIMIT : WAIT_LIMIT;
   extern __shared__ uint8_t raw_smem[];
   const uint32_t raw = smem_u32(raw_smem);
   const uint32_t base = (raw + 1023u) & ~1023u;                   // swizzled tiles start on 1024 bytes
@@ -411,6 +421,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   const int early = min(kb_count, T::STAGES);
   if (warp == 0 && lane == 0) {
     for (int i = 0; i < early; ++i) {
+      if (SELFTEST && i == p.skip_kb) continue;
       const uint32_t a_dst = base + i * T::STAGE_BYTES;
       mbar_expect_tx(full_bar(i), T::STAGE_BYTES);
       if (MODE == SWAPPED)
@@ -426,6 +437,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     if (lane == 0) {
       int issued = early;
       for (int i = 0; i < early; ++i) {          // the other operand of the stages begun above
+        if (SELFTEST && i == p.skip_kb) continue;
         const uint32_t a_dst = base + i * T::STAGE_BYTES;
         if (MODE == SWAPPED)
           tma_load_2d(a_dst + T::A_BYTES, &map_b, full_bar(i), (kb_begin + i) * BK, tile_b * BN);
@@ -434,7 +446,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       }
       for (int i = early; i < kb_count; ++i) {
         const int s = i % T::STAGES;
-        if (!mbar_wait(empty_bar(s), ((i / T::STAGES) - 1) & 1, abort_flag, p.error, 1)) break;
+        if (!mbar_wait(empty_bar(s), ((i / T::STAGES) - 1) & 1, abort_flag, p.error, 1, limit)) break;
+        if (SELFTEST && i == p.skip_kb) continue;
         const uint32_t a_dst = base + s * T::STAGE_BYTES;
         mbar_expect_tx(full_bar(s), T::STAGE_BYTES);
         tma_load_2d(a_dst, &map_a, full_bar(s), (kb_begin + i) * BK, tile_a * BM);
@@ -444,6 +457,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       if (*abort_flag) {
         // Loads that were issued still write into this block's shared memory: wait for them.
         for (int i = max(0, issued - T::STAGES); i < issued; ++i)
+          if (!(SELFTEST && i == p.skip_kb))
           for (uint32_t t = 0; t < WAIT_LIMIT && !mbar_try_wait(full_bar(i % T::STAGES), (i / T::STAGES) & 1); ++t) __nanosleep(64);
       }
     }
@@ -454,7 +468,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       bool ok = true;
       for (int i = 0; i < kb_count && ok; ++i) {
         const int s = i % T::STAGES;
-        ok = mbar_wait(full_bar(s), (i / T::STAGES) & 1, abort_flag, p.error, 2);
+        ok = mbar_wait(full_bar(s), (i / T::STAGES) & 1, abort_flag, p.error, 2, limit);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t a_addr = base + s * T::STAGE_BYTES;
@@ -474,7 +488,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     const int quadrant = warp & 3;                  // the tensor-memory lanes this warp may read
     const int row_in_tile = quadrant * 32 + lane;
     bool ok = true;
-    if (kb_count > 0) ok = mbar_wait(tmem_full_bar, 0, abort_flag, p.error, 3);
+    if (kb_count > 0) ok = mbar_wait(tmem_full_bar, 0, abort_flag, p.error, 3, SELFTEST ? 64 * limit : limit);
     ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld below needs the whole warp
     tcgen05_fence_after();
     if (ok) {
@@ -801,13 +815,13 @@ int tensor_map(CUtensorMap* out, const void* ptr, int rows, int k, int box_rows)
   return 0;
 }
 
-template <int BN, int MODE>
+template <int BN, int MODE, bool SELFTEST = false>
 int launch(const Params& p, const void* a, const void* b, int k, int splits, cudaStream_t stream) {
   using T = Tile<BN>;
   CUtensorMap map_a, map_b;
   if (int err = tensor_map(&map_a, a, p.rows_a, k, BM)) return err;
   if (int err = tensor_map(&map_b, b, p.rows_b, k, BN)) return err;
-  auto kernel = gemm_tcgen05_kernel<BN, MODE>;
+  auto kernel = gemm_tcgen05_kernel<BN, MODE, SELFTEST>;
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::SMEM_BYTES);
@@ -1009,12 +1023,12 @@ PAE_EXPORT int pae_linear_tcgen05_planes(float* partial, const void* x, const vo
 
 // How many float32 partial planes `pae_linear_tcgen05_swapped` writes for this shape.
 PAE_EXPORT int pae_linear_swapped_splits(int n, int k) {
-  // Two blocks of this form fit on each of the 148 SMs. The work should fill that one wave
+  // Two blocks of this form fit on each SM. The work should fill that one wave
   // (a second, partly filled wave costs a whole block's latency), with at least two k-blocks
   // per split. The count depends on the weight's shape alone, never on the tokens.
   const int tiles = (n + BM - 1) / BM;
   const int k_blocks = (k + BK - 1) / BK;
-  int splits = (2 * 148) / tiles;
+  int splits = (2 * sm_count()) / tiles;
   splits = splits < 1 ? 1 : splits;
   const int most = k_blocks / 2 < 1 ? 1 : k_blocks / 2;
   splits = splits > most ? most : splits;
@@ -1043,6 +1057,31 @@ PAE_EXPORT int pae_linear_tcgen05_swapped(float* partial, const void* x, const v
   if (tokens <= 32) return launch<32, SWAPPED>(p, w, x, k, splits, s);
   return launch<64, SWAPPED>(p, w, x, k, splits, s);
 }
+
+// The self-test of the give-up path: `pae_linear_tcgen05_swapped` for at most 16 tokens, except
+// that no block ever loads k-block `skip_kb` of its range. Every block's MMA issuer gives up after
+// a short wait, the error word gets its role code (2), `partial` holds nothing of use, and the
+// kernel returns by itself. Not called by the engine.
+PAE_EXPORT int pae_linear_tcgen05_selftest_giveup(float* partial, const void* x, const void* w, int tokens, int n, int k,
+                                                   int skip_kb, int* error, void* stream) {
+  if (tokens < 1 || tokens > 16 || n < 1) return fail(2, "linear_tcgen05_selftest_giveup: %d tokens (1 to 16), %d rows", tokens, n);
+  if (int err = check_operands(x, w, k)) return err;
+  const int splits = pae_linear_swapped_splits(n, k);
+  Params p{};
+  p.out = partial;
+  p.rows_a = n;
+  p.rows_b = tokens;
+  p.k_blocks = (k + BK - 1) / BK;
+  p.kb_per_split = (p.k_blocks + splits - 1) / splits;
+  if (skip_kb < 0 || skip_kb >= p.kb_per_split) return fail(2, "linear_tcgen05_selftest_giveup: k-block %d of %d", skip_kb, p.kb_per_split);
+  p.ld_out = n;
+  p.out_f32 = 1;
+  p.error = error;
+  p.skip_kb = skip_kb;
+  return launch<16, SWAPPED, true>(p, w, x, k, splits, (cudaStream_t)stream);
+}
+
+PAE_EXPORT int pae_sm_count(void) { return sm_count(); }
 
 // out[token, n] = sum over splits of partial[split, token, n] (+ bias[n]) (+ residual[token, n]),
 // summed in the order of the splits. out and residual bfloat16 or float32.

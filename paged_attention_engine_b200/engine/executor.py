@@ -16,11 +16,19 @@ from .scheduler import ScheduledWork, WorkResult
 
 
 class _TokenFuture:
-    """Sampled tokens on their way to the host: a copy into pinned memory and an event."""
+    """Sampled tokens on their way to the host: a copy into pinned memory and an event. The
+    device's error word travels in the same buffer, behind the tokens, and is looked at when
+    the tokens are: a step in which a kernel gave up on a wait raises instead of handing out
+    tokens."""
 
-    def __init__(self, tokens: torch.Tensor, host: torch.Tensor) -> None:
-        self.host = host[: tokens.numel()]
-        self.host.copy_(tokens, non_blocking=True)
+    def __init__(self, tokens: torch.Tensor, host: torch.Tensor, ops=None) -> None:
+        count = tokens.numel()
+        self.host = host[: count + 1]
+        self.host[:count].copy_(tokens, non_blocking=True)
+        self.ops = ops if hasattr(ops, "error_flag") else None
+        self.device = tokens.device
+        if self.ops is not None:
+            self.host[count:].copy_(self.ops.error_flag(self.device), non_blocking=True)
         self.event = torch.cuda.Event()
         self.event.record()
         self.values: list[int] | None = None
@@ -28,7 +36,10 @@ class _TokenFuture:
     def result(self) -> list[int]:
         if self.values is None:
             self.event.synchronize()
-            self.values = self.host.tolist()
+            values = self.host.tolist()
+            if self.ops is not None:
+                self.ops.raise_for_error_word(values[-1], self.device)
+            self.values = values[:-1]
         return self.values
 
 
@@ -43,7 +54,7 @@ class ModelExecutor:
         self.manager = runner.manager
         on_gpu = runner.runtime.device.type == "cuda"
         self.asynchronous = on_gpu if asynchronous is None else (asynchronous and on_gpu)
-        self._host_tokens = [torch.empty(1024, dtype=torch.int32).pin_memory() for _ in range(4)] if on_gpu else []
+        self._host_tokens = [torch.empty(1025, dtype=torch.int32).pin_memory() for _ in range(4)] if on_gpu else []
         self._turn = 0
 
     def begin(self, key: Hashable) -> bool:
@@ -73,7 +84,7 @@ class ModelExecutor:
         output = self.runner.step(entries, rows if rows else None)
         results = [WorkResult(None) for _ in work]
         if rows and self.asynchronous and not record_logits and len(rows) <= 1024:
-            future = _TokenFuture(output.tokens, self._host_tokens[self._turn])
+            future = _TokenFuture(output.tokens, self._host_tokens[self._turn], self.runner.runtime.ops)
             self._turn = (self._turn + 1) % len(self._host_tokens)
             at = 0
             for i, w in enumerate(work):
@@ -83,6 +94,9 @@ class ModelExecutor:
         elif rows:
             tokens = output.tokens.cpu().tolist()
             logits = output.logits.float().cpu() if record_logits else None
+            check = getattr(self.runner.runtime.ops, "check_device_errors", None)
+            if check is not None:
+                check()         # a kernel that gave up on a wait left tokens that mean nothing
             at = 0
             for i, w in enumerate(work):
                 if w.wants_token:

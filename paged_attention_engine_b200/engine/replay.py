@@ -101,6 +101,9 @@ def main(argv=None) -> int:
             return 3
         if logits is not None:
             host = logits.to(torch.float32).cpu().numpy().astype("<f4", copy=False)
+            check = getattr(engine.runtime.ops, "check_device_errors", None)
+            if check is not None:
+                check()         # a kernel that gave up on a wait: no logits are written, the program fails
             np.ascontiguousarray(host).tofile(str(out_dir / f"{record['step']}.f32"))
         print(f"done {record['step']}", flush=True)
     return 0

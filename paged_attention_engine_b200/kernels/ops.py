@@ -221,21 +221,34 @@ def _error_flag(device: torch.device) -> torch.Tensor:
     index = device.index if device.index is not None else torch.cuda.current_device()
     flag = _error_flags.get(index)
     if flag is None:
-        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):      # an ordinary tensor, whoever asks first: it is cleared from anywhere
+            flag = torch.zeros(1, dtype=torch.int32, device=device)
         _error_flags[index] = flag
     return flag
+
+
+def error_flag(device) -> torch.Tensor:
+    """The device's error word (int32 [1]): 0, or the role code of a wait that gave up. The
+    generation path copies it to the host beside the sampled tokens and hands it to
+    `raise_for_error_word`, so that a step whose kernel gave up never yields tokens silently."""
+    return _error_flag(torch.device(device))
+
+
+def raise_for_error_word(code: int, device) -> None:
+    """Raises (and clears the device's word) when `code`, a copy of the error word, is not 0."""
+    if code:
+        _error_flag(torch.device(device)).zero_()
+        index = torch.device(device).index
+        raise KernelError(
+            f"a tcgen05 kernel on device {index} gave up waiting on an mbarrier (role code {int(code)}); "
+            "its output is not valid"
+        )
 
 
 def check_device_errors() -> None:
     """Raises if a kernel gave up on a bounded wait since the last check (synchronises)."""
     for index, flag in _error_flags.items():
-        code = int(flag.item())
-        if code:
-            flag.zero_()
-            raise KernelError(
-                f"a tcgen05 kernel on device {index} gave up waiting on an mbarrier (role code {code}); "
-                "its output is not valid"
-            )
+        raise_for_error_word(int(flag.item()), flag.device)
 
 
 def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
@@ -411,37 +424,20 @@ def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int = 64, wa
     return slice_keys, -(-(max_kv_len + 15) // slice_keys)
 
 
-# Whether the slices of decode attention are merged on chip by thread-block clusters
-# (distributed shared memory, one kernel, no scratch) when there are enough (request, kv head)
-# pairs to fill the machine with 32 slices each. Measured slower than slices through scratch
-# plus a merge kernel at the benchmark's sizes (14.6 against 12.2 us per layer at batch 8,
-# context 4096), so it is off; tests run both.
-use_cluster_decode = False
-CLUSTER_DECODE_MIN_PAIRS = 8
-
-
 use_tcgen05_attention = True
 TCGEN05_ATTENTION_MIN_TOKENS = 64
-# 0: the tcgen05 attention picks its kernel by the size of the launch (two blocks of 64-key tiles
-# per SM when there are that many blocks, else one block of 128-key tiles); 1, 2 name it (tests).
-tcgen05_attention_form = 0
 
 
 def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
                       num_kv_heads, head_dim, page_size, max_kv_len, scale, window) -> None:
     """The requests that bring one token: sliced over their keys, then merged."""
     count = seqs if singles < 0 else singles
-    scratch = None
-    if use_cluster_decode and count * num_kv_heads >= CLUSTER_DECODE_MIN_PAIRS:
-        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, most=32)
-        launches = 1
-    else:
-        wave = lib.pae_decode_blocks_per_wave(c_int(head_dim))
-        slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave,
-                                                slices_per_block=lib.pae_decode_slices_per_block())
-        floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
-        scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
-        launches = 2
+    wave = lib.pae_decode_blocks_per_wave(c_int(head_dim))
+    slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave,
+                                            slices_per_block=lib.pae_decode_slices_per_block())
+    floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
+    scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
+    launches = 2
     _check(lib, lib.pae_paged_attention_decode(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
@@ -450,10 +446,16 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
 
 
 def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
-                    page_size, max_q_len, max_kv_len, scale, window, num_single=None) -> torch.Tensor:
+                    page_size, max_q_len, max_kv_len, scale, window, num_single=None, form: int = 0,
+                    info: dict | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages. `num_single` is the number
     of requests that bring exactly one token when the caller knows it (it decides which kernels
-    are launched; None launches whatever may be needed)."""
+    are launched; None launches whatever may be needed). `form` 0 lets the tcgen05 attention pick
+    its kernel by the size of the launch (two blocks of 64-key tiles per SM when there are that
+    many blocks, else one block of 128-key tiles, its keys shared out over a cluster when the
+    blocks are few); 1, 2, 4, 8, 16 name the kernel (tests). `info`, when given, receives which
+    kernel ran ("kernel") and, for tcgen05, the blocks per query tile ("cluster": 0 is the
+    paired kernel)."""
     qkv = materialized(qkv)
     _need(qkv, "paged_attention: qkv")
     _need(keys, "paged_attention: keys", qkv.dtype)
@@ -472,17 +474,22 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
             tc5 = _lib("attention_tcgen05")
             if tc5.pae_attention_tcgen05_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
                 decode_after = mma_ok and singles != 0
+                chosen = c_int(-1)
                 _check(tc5, tc5.pae_paged_attention_prefill_tcgen05(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), ctypes.c_longlong(keys.shape[0]), _ptr(block_table),
                     c_int(block_table.shape[1]), _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(tokens), c_int(seqs),
                     c_int(max_q_len), c_int(max_kv_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
-                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), c_int(singles), c_int(tcgen05_attention_form),
-                    _ptr(_error_flag(qkv.device)), _stream()))
+                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), c_int(singles), c_int(form),
+                    ctypes.byref(chosen), _ptr(_error_flag(qkv.device)), _stream()))
+                if info is not None:
+                    info.update(kernel="tcgen05", cluster=chosen.value)
                 if decode_after:
                     _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles,
                                       num_heads, num_kv_heads, head_dim, page_size, max_kv_len, scale, window)
                 return out
         if mma_ok:
+            if info is not None:
+                info.update(kernel="mma")
             if max_q_len > 1:
                 _check(lib, lib.pae_paged_attention_prefill(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
@@ -493,6 +500,8 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
                 _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
                                   num_kv_heads, head_dim, page_size, max_kv_len, scale, window)
             return out
+    if info is not None:
+        info.update(kernel="simt")
     lib = _lib("attention_simt")
     _check(lib, lib.pae_paged_attention_simt(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),

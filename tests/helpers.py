@@ -231,16 +231,48 @@ def max_live_tokens(trace: list[dict], page: int = 64) -> int:
     return worst
 
 
-def run_in_process(folder: Path, dtype: str, trace: list[dict], max_tokens: int, block_size: int, ops=None, device="cuda:0"):
-    """Replays a trace through the engine's Replayer in this process; returns (outputs, replayer)."""
+def fragment_pool(manager, seed: int) -> None:
+    """Leaves every group's free list in a shuffled order (the reference's `_fragment_pool`,
+    tests/test_parity.py:196-223): placeholder requests take every page, one page each round
+    robin, and give them back in a seeded random order; freed pages queue up at the back, so
+    the next requests get pages that are neither adjacent nor ascending."""
+    rng = random.Random(seed)
+    holders = [f"__fragment_{i}" for i in range(manager.slots.num_free)]
+    for key in holders:
+        assert manager.create_request(key) is not None
+    taken = True
+    while taken:
+        taken = False
+        for key in holders:
+            if manager.num_free > 0 and manager.reserve(key, manager.block_size).ok:
+                taken = True
+    assert manager.num_free == 0
+    rng.shuffle(holders)
+    for key in holders:
+        manager.free_request(key)
+    assert manager.num_free == manager.num_blocks
+
+
+def run_in_process(folder: Path, dtype: str, trace: list[dict], max_tokens: int, block_size: int, ops=None, device="cuda:0",
+                   prepare=None, watch=None):
+    """Replays a trace through the engine's Replayer in this process; returns (outputs, replayer).
+    `prepare(replayer)` runs before the first step, `watch(replayer, record)` after every step and
+    before the step's finished requests give their pages back."""
     from paged_attention_engine_b200.engine.llm import Engine
     from paged_attention_engine_b200.engine.replay import Replayer
 
     engine = Engine.from_pretrained(folder, dtype, device=device, ops=ops)
     replayer = Replayer(engine, max_tokens, block_size)
+    if prepare is not None:
+        prepare(replayer)
     outputs = {}
     for record in trace:
-        logits = replayer.run(record)
+        if watch is None:
+            logits = replayer.run(record)
+        else:
+            logits = replayer.run(dict(record, end=[]))
+            watch(replayer, record)
+            replayer.run({"step": record["step"], "entries": [], "end": record.get("end", [])})
         if logits is not None:
             outputs[record["step"]] = logits.float().cpu()
     return outputs, replayer

@@ -50,15 +50,42 @@ def test_many_tokens(ops, m, n, k, extras):
     _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
 
 
-@pytest.mark.parametrize("m,n,k,planes", [(65, 1536, 8960, 16), (128, 1536, 8960, 16), (300, 1536, 8960, 5), (1024, 1536, 8960, 2),
-                                          (130, 520, 2056, 4), (2048, 1536, 8960, 1), (128, 1536, 1536, 1)])
+def _expected_planes(m, n, k, sms):
+    """The rule of `pae_linear_tcgen05_plane_count`, restated: as many K ranges per output tile as
+    fill the SMs, each of at least 8 k-blocks of 64; 1 when the tiles fill half of the SMs by
+    themselves, when K is short, or for few tokens or narrow outputs."""
+    up = lambda a, b: -(-a // b)
+    k_blocks = up(k, 64)
+    if m <= 64 or n < 256 or k_blocks < 32:
+        return 1
+    tiles_a = up(m, 128)
+    width = min((256, 192, 176), key=lambda w: (up(tiles_a * up(n, w), sms) * (w + 32), -w))
+    tiles = tiles_a * up(n, width)
+    if tiles * 2 > sms:
+        return 1
+    planes = min(sms // tiles, k_blocks // 8)
+    if planes < 2:
+        return 1
+    return up(k_blocks, up(k_blocks, planes))
+
+
+def test_the_plane_rule_at_148_sms():
+    """What the rule gives on a B200 (148 SMs), as a record of the sizes it was tuned at."""
+    cases = [(65, 1536, 8960, 16), (128, 1536, 8960, 16), (300, 1536, 8960, 5), (1024, 1536, 8960, 2),
+             (130, 520, 2056, 4), (2048, 1536, 8960, 1), (128, 1536, 1536, 1)]
+    assert [_expected_planes(m, n, k, 148) for m, n, k, _ in cases] == [p for *_, p in cases]
+
+
+@pytest.mark.parametrize("m,n,k", [(65, 1536, 8960), (128, 1536, 8960), (300, 1536, 8960), (1024, 1536, 8960),
+                                   (130, 520, 2056), (2048, 1536, 8960), (128, 1536, 1536), (200, 3584, 18944), (100, 5120, 27648)])
 @pytest.mark.parametrize("extras", [(False, False), (True, True)])
-def test_few_output_tiles_and_a_long_k_share_k_over_blocks(ops, m, n, k, planes, extras):
+def test_few_output_tiles_and_a_long_k_share_k_over_blocks(ops, m, n, k, extras):
     """A down projection for a few hundred tokens has a handful of output tiles: each tile's K
     is shared out over blocks that write float32 planes, which the consumer adds up. The plane
-    count is what fills the SMs (for 148 of them), 1 when the tiles do already or K is short."""
+    count is what fills this device's SMs, 1 when the tiles do already or K is short."""
     lib = ops._lib("gemm_tcgen05")
     import ctypes
+    planes = _expected_planes(m, n, k, lib.pae_sm_count())
     assert lib.pae_linear_tcgen05_plane_count(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k)) == planes
     x = _rand((m, k), 1)
     w = _rand((n, k), 2, 0.05)
@@ -67,6 +94,37 @@ def test_few_output_tiles_and_a_long_k_share_k_over_blocks(ops, m, n, k, planes,
     if planes > 1:
         assert tuple(pending.partial.shape) == (planes, m, n)
     _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(ops):
+    """The kernels' only failure detection is the bounded wait on an mbarrier. The self-test
+    kernel is the few-token product whose producer never loads one k-block (nothing is in
+    flight for it): the MMA issuer's wait for that stage runs out after a few thousand polls, the
+    block leaves by its give-up path (loads in flight waited for, tensor memory freed), and
+    the error word holds the role's code. Afterwards the context is intact and an ordinary
+    product is right."""
+    import ctypes
+    from ctypes import c_int, c_void_p
+
+    lib = ops._lib("gemm_tcgen05")
+    m, n, k = 8, 2048, 1536
+    x = _rand((m, k), 1)
+    w = _rand((n, k), 2, 0.05)
+    ops.check_device_errors()
+    splits = lib.pae_linear_swapped_splits(c_int(n), c_int(k))
+    partial = torch.zeros((splits, m, n), dtype=torch.float32, device="cuda")
+    flag = ops.error_flag("cuda:0")
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = lib.pae_linear_tcgen05_selftest_giveup(c_void_p(partial.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
+                                                  c_int(m), c_int(n), c_int(k), c_int(1), c_void_p(flag.data_ptr()), stream)
+    assert code == 0, lib.pae_last_error().decode()
+    torch.cuda.synchronize()                     # the kernel came back by itself
+    assert int(flag.item()) == 2, "the MMA issuer's wait (role 2) is the one that runs out"
+    with pytest.raises(ops.KernelError, match="role code 2"):
+        ops.check_device_errors()
+    ops.check_device_errors()                    # the word was cleared
+    _check(ops, m, n, k, bias=True, residual=True, out_dtype=torch.bfloat16)
+    _check(ops, 300, n, k, bias=True, residual=False, out_dtype=torch.bfloat16)
 
 
 @pytest.mark.parametrize("m,n,k", [(4, 151936, 1536), (70, 3001, 520), (8, 509, 96)])

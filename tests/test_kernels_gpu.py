@@ -169,10 +169,14 @@ def test_sampling(ops, vocab):
     # The device's float32 scores may order two near-equal candidates otherwise than the
     # float64 restatement: the token drawn must score within 1e-4 of the restatement's best.
     from plain import qwen2_plain as plain
-    if vocab <= 509:
-        for r in range(2, 5):
-            scores = plain.sample_scores(logits[r], float(temperature[r]), int(seed[r]), int(key[r]), int(index[r]))
-            assert scores[got[r]].item() >= scores.max().item() - 1e-4
+    for r in range(2, 5):
+        # the vectorised restatement at every vocabulary (at 151,936 the draw is two kernels and scratch) ...
+        scores = ref.gumbel_scores(logits[r], float(temperature[r]), lo[r], hi[r], key[r], index[r])
+        assert scores[got[r]].item() >= scores.max().item() - 1e-4, f"row {r}: drew {int(got[r])}, the best is {int(scores.argmax())}"
+        if vocab <= 509:
+            # ... which the plain implementation's entry-by-entry one agrees with
+            slow = plain.sample_scores(logits[r], float(temperature[r]), int(seed[r]), int(key[r]), int(index[r]))
+            assert (slow - scores).abs().max().item() <= 1e-9
 
 
 def _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, dtype, spike=True, late_spike=False):
@@ -222,16 +226,13 @@ def test_short_portions_over_long_contexts_share_their_keys_over_a_cluster(ops, 
     args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
                 max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
     want = ref.paged_attention(*tensors, **args)
-    got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+    info = {}
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args, info=info)
     ops.check_device_errors()
-    assert ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster() >= (2 if window else 4)
+    assert info["kernel"] == "tcgen05" and info["cluster"] >= (2 if window else 4), info
     _close(got, want, torch.bfloat16, scale=2.0)
-    ops.tcgen05_attention_form = 1
-    try:
-        alone = ops.paged_attention(*[t.cuda() for t in tensors], **args)
-    finally:
-        ops.tcgen05_attention_form = 0
-    assert ops._lib("attention_tcgen05").pae_attention_tcgen05_last_cluster() == 1
+    alone = ops.paged_attention(*[t.cuda() for t in tensors], **args, form=1, info=info)
+    assert info["cluster"] == 1
     assert (got.float() - alone.float()).abs().max().item() <= 2.0 ** -6 * float(alone.float().abs().max())
 
 
@@ -248,14 +249,6 @@ def test_decode_attention_over_long_contexts(ops, heads, kv_heads, d, page, wind
     want = ref.paged_attention(*tensors, **args)
     got = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=len(kv))
     _close(got, want, torch.bfloat16, scale=2.0)
-    # The slices merged on chip by a cluster, and merged through scratch by a second kernel.
-    ops.use_cluster_decode = True
-    try:
-        other = ops.paged_attention(*[t.cuda() for t in tensors], **args, num_single=len(kv))
-    finally:
-        ops.use_cluster_decode = False
-    _close(other, want, torch.bfloat16, scale=2.0)
-    assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -7 * float(want.abs().max())
 
 
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [
@@ -314,11 +307,9 @@ def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window, form, 
                 max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
     want = ref.paged_attention(*tensors, **args)
     assert ops.use_tcgen05_attention
-    ops.tcgen05_attention_form = form
-    try:
-        got = ops.paged_attention(*[t.cuda() for t in tensors], **args)
-    finally:
-        ops.tcgen05_attention_form = 0
+    info = {}
+    got = ops.paged_attention(*[t.cuda() for t in tensors], **args, form=form, info=info)
+    assert info["kernel"] == "tcgen05" and (form == 0 or info["cluster"] == {1: 1, 2: 0}.get(form, form // 2)), info
     ops.check_device_errors()
     _close(got, want, torch.bfloat16, scale=2.0)
     ops.use_tcgen05_attention = False
@@ -327,3 +318,50 @@ def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window, form, 
     finally:
         ops.use_tcgen05_attention = True
     assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -6 * float(other.float().abs().max())
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [(4, 2, 128, 16, 100), (6, 3, 64, 32, 70), (2, 1, 128, 16, 257), (4, 4, 64, 16, 33)])
+@pytest.mark.parametrize("form", ["mma", 1, 2, 0])
+def test_windowed_attention_over_a_table_with_released_pages(ops, heads, kv_heads, d, page, window, form):
+    """A windowed layer as the cache manager leaves it: the table entries of the pages that the
+    window has passed are -1 and the pages themselves hold something else by now (here: NaN, as
+    do all pages that no request owns). No kernel may read through such an entry, whichever tile
+    size it rounds the window's first key down to."""
+    gen = torch.Generator().manual_seed(41)
+    q_lens = [200, 1, 70, 1, 129, 64]
+    pos0 = [300, 500, 1000, 90, 64, 37]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16)
+    qkv, keys, values, table, q_start, q_pos0, kv_len = tensors
+    owned = set()
+    for b, p0 in enumerate(pos0):
+        released = max(p0 - window + 1, 0) // page          # what CacheManager.advance gives back before this step
+        table[b, :released] = -1
+        owned |= {int(x) for x in table[b] if x >= 0}
+    for pid in range(keys.shape[0]):
+        if pid not in owned:
+            keys[pid] = float("nan")
+            values[pid] = float("nan")
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window)
+    want = ref.paged_attention(*tensors, **args)
+    assert torch.isfinite(want).all()
+    info = {}
+    if form == "mma":
+        ops.use_tcgen05_attention = False
+    try:
+        got = ops.paged_attention(*[t.cuda() for t in tensors], **args, form=0 if form == "mma" else form, info=info)
+    finally:
+        ops.use_tcgen05_attention = True
+    assert info["kernel"] == ("mma" if form == "mma" else "tcgen05"), info
+    ops.check_device_errors()
+    assert torch.isfinite(got).all(), "a kernel read a page that the table no longer names"
+    _close(got, want, torch.bfloat16, scale=2.0)
+    # the CUDA-core kernel in both dtypes
+    ops.use_tensor_cores = False
+    try:
+        slow = ops.paged_attention(*[t.cuda() for t in tensors], **args)
+        slow32 = ops.paged_attention(*[t.cuda().float() if t.is_floating_point() else t.cuda() for t in tensors], **args)
+    finally:
+        ops.use_tensor_cores = True
+    assert torch.isfinite(slow).all() and torch.isfinite(slow32).all()
+    _close(slow, want, torch.bfloat16, scale=2.0)

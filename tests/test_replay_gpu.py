@@ -65,6 +65,35 @@ def test_mixed_with_reuse(case):
         assert allocator.num_free == allocator.num_blocks
 
 
+def test_mixed_on_a_fragmented_pool(case):
+    """The mixed replay again, started on a pool whose free list is shuffled: the requests' pages
+    are neither adjacent nor ascending (asserted: some block table must be non-monotonic, as in
+    the reference's tests/test_parity.py:318-321), and the logits are those of the plain model."""
+    folder, raw, page, dtype_name, requests, oracle = case
+    trace = helpers.trace_mixed(requests, seed=17)
+    budget = helpers.max_live_tokens(trace)
+    tables = []
+
+    def watch(replayer, record):
+        for key in replayer.manager.live_requests():
+            for group in range(len(replayer.manager.allocators)):
+                tables.append(replayer.manager.block_table(key, group))
+
+    outputs, replayer = helpers.run_in_process(
+        folder, dtype_name, trace, budget, page, prepare=lambda r: helpers.fragment_pool(r.manager, seed=3), watch=watch)
+    got = helpers.collect(trace, outputs, requests)
+    for key in requests:
+        gap = (got[key] - oracle[key]).abs().max().item()
+        assert gap <= helpers.tolerance(DTYPES[dtype_name], oracle[key]), f"{key}: {gap}"
+    long_tables = [[p for p in t if p >= 0] for t in tables]
+    long_tables = [t for t in long_tables if len(t) >= 3]
+    assert long_tables, "no request held three pages at once"
+    assert any(t != sorted(t) for t in long_tables), "every block table was ascending: the pool was not fragmented"
+    assert any(max(abs(a - b) for a, b in zip(t, t[1:])) > 1 for t in long_tables), "all pages were adjacent"
+    for allocator in replayer.manager.allocators:
+        assert allocator.num_free == allocator.num_blocks
+
+
 def test_cuts_agree_with_each_other(case):
     """The same tokens cut in two ways give the same logits up to the rounding of sums."""
     folder, raw, page, dtype_name, requests, oracle = case

@@ -123,20 +123,25 @@ def _mix32(x):
     return x
 
 
+def gumbel_scores(row, t, seed_lo, seed_hi, request_key, output_index):
+    """float64 [vocab]: logits / t + Gumbel noise of the row's counters, every entry at once."""
+    vocab = torch.arange(row.shape[0], dtype=torch.int64)
+    h = _mix32((int(seed_lo) & _M32) ^ 0x9E3779B9)
+    h = _mix32(h ^ (int(seed_hi) & _M32))
+    h = _mix32(h + (int(request_key) & _M32) * 0x7FEB352D)
+    h = _mix32(h + (int(output_index) & _M32) * 0x846CA68B)
+    hv = _mix32((h + ((vocab * 0x9E3779B1) & _M32)) & _M32)
+    u = ((hv >> 9).double() + 0.5) / 8388608.0
+    return row.double().cpu() / t - torch.log(-torch.log(u))
+
+
 def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index):
     """Per row: argmax for temperature 0, else Gumbel-max with the engine's counter-based noise."""
     out = torch.empty(logits.shape[0], dtype=torch.int32)
-    vocab = torch.arange(logits.shape[1], dtype=torch.int64)
     for r in range(logits.shape[0]):
         t = float(temperature[r])
         row = logits[r].double().cpu()
         if t > 0.0:
-            h = _mix32((int(seed_lo[r]) & _M32) ^ 0x9E3779B9)
-            h = _mix32(h ^ (int(seed_hi[r]) & _M32))
-            h = _mix32(h + (int(request_key[r]) & _M32) * 0x7FEB352D)
-            h = _mix32(h + (int(output_index[r]) & _M32) * 0x846CA68B)
-            hv = _mix32((h + ((vocab * 0x9E3779B1) & _M32)) & _M32)
-            u = ((hv >> 9).double() + 0.5) / 8388608.0
-            row = row / t - torch.log(-torch.log(u))
+            row = gumbel_scores(logits[r], t, seed_lo[r], seed_hi[r], request_key[r], output_index[r])
         out[r] = int(torch.argmax(row))
     return out
