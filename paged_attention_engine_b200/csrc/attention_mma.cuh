@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(SLICE_WARPS * 32) decode_slices_kernel(const D
   const int* table = p.block_table + (size_t)b * p.table_width;
 
   auto fetch = [&](int stage, int key0) {
-    const int page = table[key0 / p.page_size];
+    const int page = checked_page(table[checked_table_index(key0 / p.page_size, p.table_width)]);
     const size_t row0 = ((size_t)page * p.kv_heads + g) * p.page_size + (key0 % p.page_size);
     const uint32_t k_dst = mine_u32 + stage * 2 * TILE_BYTES;
     constexpr int CHUNKS = TILE_KEYS * D / 8;
@@ -533,12 +533,13 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
       if (key < kv_end) {
         int page, offset;
         if (page_shift >= 0) {
-          page = table[key >> page_shift];
+          page = table[checked_table_index(key >> page_shift, p.table_width)];
           offset = key & (p.page_size - 1);
         } else {
-          page = table[key / p.page_size];
+          page = table[checked_table_index(key / p.page_size, p.table_width)];
           offset = key % p.page_size;
         }
+        page = checked_page(page);
         const size_t src = (size_t)page * page_stride + head_offset + (size_t)offset * D;
         cp_async16(k_dst + dst_offset[j], p.keys + src);
         cp_async16(k_dst + TILE_BYTES + dst_offset[j], p.values + src);

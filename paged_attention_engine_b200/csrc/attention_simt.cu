@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(THREADS) paged_attention_simt_kernel(
     for (int c = warp; c < BKEYS; c += THREADS / 32) {
       const int j = base + c;
       if (j < kv_end) {
-        const int page = table[j / page_size];
+        const int page = checked_page(table[checked_table_index(j / page_size, table_width)]);
         const size_t at = (((size_t)page * kv_heads + g) * page_size + (j % page_size)) * d;
         for (int k = lane; k < d; k += 32) {
           ks[c * dpad + k] = to_float(keys[at + k]);

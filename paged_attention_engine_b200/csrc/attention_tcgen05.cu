@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   const int last_page = working ? (kv_end - 1) / p.page_size : 0;    // the last page that holds a visible key
   int first_page = 0;
   if (warp == 0 && working && lane < BKEYS / p.page_size)
-    first_page = p.block_table[(size_t)b * p.table_width + min(kv_begin / p.page_size + lane, last_page)];
+    first_page = checked_page(p.block_table[(size_t)b * p.table_width + checked_table_index(min(kv_begin / p.page_size + lane, last_page), p.table_width)]);
   dependent_launch_wait();
 
   if (warp == 0) {
@@ -337,7 +337,8 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
       for (int t = 0; t < n_tiles; ++t) {
         const int st = t & 1;
         int next_page = 0;
-        if (mine && t + 1 < n_tiles) next_page = table[min((kv_begin + (t + 1) * BKEYS) / p.page_size + lane, last_page)];
+        if (mine && t + 1 < n_tiles)
+          next_page = checked_page(table[checked_table_index(min((kv_begin + (t + 1) * BKEYS) / p.page_size + lane, last_page), p.table_width)]);
         if (t >= 2) {
           if (lane == 0) ok = mbar_wait(bar(K_EMPTY, st), ((t >> 1) - 1) & 1, abort_flag, p.error, 1);
           ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -757,8 +758,8 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
   const int window_page = first_key / p.page_size;
   int first_page = 0;
   if (warp == 0 && active && lane < BKEYS / box_rows)
-    first_page = p.block_table[(size_t)b * p.table_width +
-                               max(min((kv_begin + lane * box_rows) / p.page_size, last_page), window_page)];
+    first_page = checked_page(p.block_table[(size_t)b * p.table_width +
+                                            checked_table_index(max(min((kv_begin + lane * box_rows) / p.page_size, last_page), window_page), p.table_width)]);
   dependent_launch_wait();
 
   if (warp == 0) {
@@ -782,7 +783,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
       // the request will do; the last visible one is taken.
       auto box_row = [&](int t) {
         const int key = kv_begin + t * BKEYS + lane * box_rows;
-        const int page = table[max(min(key / p.page_size, last_page), window_page)];
+        const int page = checked_page(table[checked_table_index(max(min(key / p.page_size, last_page), window_page), p.table_width)]);
         return (page * p.kv_heads + g) * p.page_size + key % p.page_size;
       };
       int row = mine ? (first_page * p.kv_heads + g) * p.page_size + (kv_begin + lane * box_rows) % p.page_size : 0;

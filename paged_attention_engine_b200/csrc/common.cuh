@@ -64,6 +64,57 @@ __device__ __forceinline__ void rotate_pair(float& lo, float& hi, float c, float
   hi = new_hi;
 }
 
+// ---------------------------------------------------------------------------------------
+// The checked build (-DPAE_BOUNDS, `PAE_BOUNDS=1` for kernels/build.py): every slot, block-table
+// index and page id that a kernel takes from the step's integer arrays is compared with what
+// the cache holds before it becomes an address. A value out of range sets the device's error
+// word (101: a slot beyond the pool; 102: a block-table index beyond the table's width; 103: a
+// page id that is negative or beyond the pool) and the access is not made: a write is
+// skipped, a read goes to page 0 instead. Nothing traps; the host reads the word like that of a
+// wait that gave up. In the ordinary build the helpers below are the identity and cost nothing.
+// The limits reach a library through `pae_set_bounds(pages, error word)`.
+// ---------------------------------------------------------------------------------------
+#ifdef PAE_BOUNDS
+struct Bounds {
+  long long pages;
+  int* error;
+};
+__device__ Bounds g_bounds = {0, nullptr};
+__device__ __forceinline__ void bounds_violation(int code) {
+  if (g_bounds.error != nullptr) atomicCAS(g_bounds.error, 0, code);
+}
+#endif
+
+__device__ __forceinline__ bool slot_in_pool(int slot, int page_size) {
+#ifdef PAE_BOUNDS
+  if (g_bounds.pages > 0 && (slot < 0 || (long long)(slot / page_size) >= g_bounds.pages)) {
+    bounds_violation(101);
+    return false;
+  }
+#endif
+  return true;
+}
+
+__device__ __forceinline__ int checked_table_index(int index, int width) {
+#ifdef PAE_BOUNDS
+  if (index < 0 || index >= width) {
+    bounds_violation(102);
+    return 0;
+  }
+#endif
+  return index;
+}
+
+__device__ __forceinline__ int checked_page(int page) {
+#ifdef PAE_BOUNDS
+  if (g_bounds.pages > 0 && (page < 0 || (long long)page >= g_bounds.pages)) {
+    bounds_violation(103);
+    return 0;
+  }
+#endif
+  return page;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -142,6 +193,17 @@ inline void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 bloc
 
 #define PAE_EXPORT extern "C" __attribute__((visibility("default")))
 
-// Each library exports its own message getter.
+// Each library exports its own message getter (and, in the checked build, the setter of its limits).
+#ifdef PAE_BOUNDS
+#define PAE_DEFINE_LAST_ERROR()                                                                     \
+  PAE_EXPORT const char* pae_last_error() { return pae::error_buffer(); }                           \
+  PAE_EXPORT int pae_set_bounds(long long pages, int* error) {                                      \
+    pae::Bounds b{pages, error};                                                                    \
+    cudaError_t err = cudaMemcpyToSymbol(pae::g_bounds, &b, sizeof(b));                             \
+    if (err != cudaSuccess) return pae::fail(100, "set_bounds: %s", cudaGetErrorString(err));       \
+    return 0;                                                                                       \
+  }
+#else
 #define PAE_DEFINE_LAST_ERROR() \
   PAE_EXPORT const char* pae_last_error() { return pae::error_buffer(); }
+#endif

@@ -267,7 +267,7 @@ __global__ void rotary_qk_cache_write_kernel(T* __restrict__ qkv, const float* _
   }
   if (head >= heads && slots != nullptr) {
     const int slot = slots[t];
-    if (slot < 0) return;
+    if (slot < 0 || !slot_in_pool(slot, page_size)) return;
     const int page = slot / page_size, offset = slot - page * page_size;
     const bool is_key = head < heads + kv_heads;
     const int kv_head = is_key ? head - heads : head - heads - kv_heads;

@@ -247,7 +247,7 @@ __global__ void splitk_rotary_cache_write_kernel(T* __restrict__ qkv, const floa
   }
   qkv[at + f] = from_float<T>(lo);
   qkv[at + f + half] = from_float<T>(hi);
-  if (slot >= 0) {
+  if (slot >= 0 && slot_in_pool(slot, page_size)) {
     const int page = slot / page_size, offset = slot - page * page_size;
     const bool is_key = head < heads + kv_heads;
     const int kv_head = is_key ? head - heads : head - heads - kv_heads;

@@ -338,7 +338,7 @@ __device__ __forceinline__ void store_rotary_chunks(const Params& p, int row, in
   *(uint4*)(out + col_hi) = packed[2];
   *(uint4*)(out + col_hi + 8) = packed[3];
   if (head >= p.heads) {
-    if (slot >= 0) {
+    if (slot >= 0 && slot_in_pool(slot, p.page_size)) {
       const int page = slot / p.page_size, offset = slot - page * p.page_size;
       const bool is_key = head < p.heads + p.kv_heads;
       const int kv_head = is_key ? head - p.heads : head - p.heads - p.kv_heads;

@@ -61,7 +61,9 @@ class ModelRunner:
             self.manager, self.runtime.ops, self.runtime.dtype, self.runtime.device, model.spec.vocab_size
         )
         self.entry_caches = [cache.entry_cache(p) for p in range(len(model.spec.schedule))]
-        self.use_graphs = use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
+        # The checked build hands its limits to the libraries between launches: it records no graphs.
+        self.use_graphs = (use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
+                           and not getattr(self.runtime.ops, "bounds_checked", False))
         self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
         self.graph_pool = None
         self.capture_stream = None

@@ -44,6 +44,12 @@ FAMILIES: dict[str, list[str]] = {
     ],
 }
 
+# The checked build: `PAE_BOUNDS=1` in the environment compiles every family with -DPAE_BOUNDS
+# (slots, block-table indices and page ids are range-checked on the device before they become
+# addresses; see csrc/common.cuh). Its libraries carry `checked` in their names and live beside
+# the ordinary ones.
+BOUNDS = os.environ.get("PAE_BOUNDS", "0") not in ("", "0")
+
 _lock = threading.Lock()
 
 
@@ -81,24 +87,34 @@ def build_dir() -> Path:
         return fallback
 
 
-def family_hash(name: str) -> str:
+def nvcc_flags(bounds: bool | None = None) -> list[str]:
+    bounds = BOUNDS if bounds is None else bounds
+    return NVCC_FLAGS + (["-DPAE_BOUNDS"] if bounds else [])
+
+
+def family_hash(name: str, bounds: bool | None = None) -> str:
     digest = hashlib.sha256()
     for source in FAMILIES[name]:
         digest.update(source.encode())
         digest.update((CSRC / source).read_bytes())
-    digest.update(" ".join(NVCC_FLAGS).encode())
+    digest.update(" ".join(nvcc_flags(bounds)).encode())
     return digest.hexdigest()[:12]
 
 
-def library_path(name: str, folder: Path | None = None) -> Path:
-    return (folder or build_dir()) / f"libpae_{name}_{family_hash(name)}.so"
+def _stem(name: str, bounds: bool | None = None) -> str:
+    bounds = BOUNDS if bounds is None else bounds
+    return f"libpae_{name}_checked" if bounds else f"libpae_{name}"
 
 
-def _compile(name: str, target: Path) -> None:
+def library_path(name: str, folder: Path | None = None, bounds: bool | None = None) -> Path:
+    return (folder or build_dir()) / f"{_stem(name, bounds)}_{family_hash(name, bounds)}.so"
+
+
+def _compile(name: str, target: Path, bounds: bool | None = None) -> None:
     nvcc = find_nvcc()
     source = CSRC / FAMILIES[name][0]
     partial = target.with_suffix(f".tmp{os.getpid()}.so")
-    command = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-o", str(partial), str(source)]
+    command = [nvcc, *nvcc_flags(bounds), "-I", str(CSRC), "-o", str(partial), str(source)]
     say(f"compiling {source.name} for sm_100a ...")
     started = time.time()
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
@@ -112,24 +128,24 @@ def _compile(name: str, target: Path) -> None:
         partial.unlink(missing_ok=True)
         raise RuntimeError(f"nvcc failed on {source.name}:\n{output}")
     os.replace(partial, target)
-    for stale in target.parent.glob(f"libpae_{name}_????????????.so"):
+    for stale in target.parent.glob(f"{_stem(name, bounds)}_????????????.so"):
         if stale != target:
             stale.unlink(missing_ok=True)      # an older build of the same family
     say(f"built {target.name} in {time.time() - started:.0f} s")
 
 
-def ensure_built(names: list[str]) -> dict[str, Path]:
+def ensure_built(names: list[str], bounds: bool | None = None) -> dict[str, Path]:
     """Paths of the libraries of the given families, compiling those that are missing."""
     with _lock:
         folder = build_dir()
-        paths = {n: library_path(n, folder) for n in names}
+        paths = {n: library_path(n, folder, bounds) for n in names}
         missing = [n for n in names if not paths[n].is_file()]
         if missing:
             errors: list[BaseException] = []
 
             def work(n: str) -> None:
                 try:
-                    _compile(n, paths[n])
+                    _compile(n, paths[n], bounds)
                 except BaseException as exc:  # noqa: BLE001  (reported below)
                     errors.append(exc)
 
@@ -143,5 +159,5 @@ def ensure_built(names: list[str]) -> dict[str, Path]:
         return paths
 
 
-def build_all() -> dict[str, Path]:
-    return ensure_built(list(FAMILIES))
+def build_all(bounds: bool | None = None) -> dict[str, Path]:
+    return ensure_built(list(FAMILIES), bounds)

@@ -25,8 +25,30 @@ _libs: dict[str, ctypes.CDLL] = {}
 launches = 0
 
 
+# True when the libraries are the checked build (PAE_BOUNDS=1: see kernels/build.py). The kernels
+# then compare every slot, block-table index and page id with the pool before using it; the
+# limits are handed to a library whenever they change, which a recorded graph cannot follow, so
+# the runner records none in this mode.
+bounds_checked = build.BOUNDS
+_bounds_set: dict[str, tuple] = {}
+
+
 class KernelError(RuntimeError):
     pass
+
+
+def _set_bounds(name: str, pages_of: torch.Tensor | None) -> None:
+    """Checked build only: tells library `name` how many pages the pool of `pages_of` has."""
+    if not bounds_checked or pages_of is None:
+        return
+    flag = _error_flag(pages_of.device)
+    limits = (int(pages_of.shape[0]), flag.data_ptr())
+    if _bounds_set.get(name) != limits:
+        lib = _lib(name)
+        code = lib.pae_set_bounds(ctypes.c_longlong(limits[0]), c_void_p(limits[1]))
+        if code != 0:
+            raise KernelError(lib.pae_last_error().decode(errors="replace"))
+        _bounds_set[name] = limits
 
 
 def require_cuda() -> None:
@@ -239,6 +261,10 @@ def raise_for_error_word(code: int, device) -> None:
     if code:
         _error_flag(torch.device(device)).zero_()
         index = torch.device(device).index
+        if int(code) >= 100:
+            what = {101: "a slot beyond the pool", 102: "a block-table index beyond the table's width",
+                    103: "a page id that is negative or beyond the pool"}.get(int(code), "an index out of range")
+            raise KernelError(f"a kernel on device {index} met {what} (bounds code {int(code)}); the access was skipped")
         raise KernelError(
             f"a tcgen05 kernel on device {index} gave up waiting on an mbarrier (role code {int(code)}); "
             "its output is not valid"
@@ -353,6 +379,7 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         splits = qkv.partial.shape[0]
         out = torch.empty((tokens, width), dtype=qkv.dtype, device=qkv.device)
         lib = _lib("fused_decode")
+        _set_bounds("fused_decode", keys if slots is not None else None)
         _check(lib, lib.pae_splitk_rotary_cache_write(
             _ptr(out), _ptr(qkv.partial), c_int(splits), _ptr(qkv.bias), _ptr(table), _ptr(slots), key_ptr, value_ptr,
             c_int(tokens), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
@@ -362,6 +389,7 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
     qkv = materialized(qkv)
     _need(qkv, "rotary_qk_cache_write: qkv")
     lib = _lib("elementwise")
+    _set_bounds("elementwise", keys if slots is not None else None)
     _check(lib, lib.pae_rotary_qk_cache_write(
         _ptr(qkv), _ptr(table), _ptr(slots), key_ptr, value_ptr, c_int(tokens), c_int(num_heads), c_int(num_kv_heads),
         c_int(head_dim), c_int(page_size), c_int(_code(qkv)), _stream()))
@@ -399,6 +427,7 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
                 _need(keys, "qkv_projection: keys", torch.bfloat16)
                 _need(values, "qkv_projection: values", torch.bfloat16)
             out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+            _set_bounds("gemm_tcgen05", keys if slots is not None else None)
             _check(lib, lib.pae_linear_rotary_tcgen05(
                 _ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(table), _ptr(slots),
                 _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), c_int(m),
@@ -438,6 +467,7 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
     floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
     scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
     launches = 2
+    _set_bounds("attention_mma", keys)
     _check(lib, lib.pae_paged_attention_decode(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
@@ -475,6 +505,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
             if tc5.pae_attention_tcgen05_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
                 decode_after = mma_ok and singles != 0
                 chosen = c_int(-1)
+                _set_bounds("attention_tcgen05", keys)
                 _check(tc5, tc5.pae_paged_attention_prefill_tcgen05(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), ctypes.c_longlong(keys.shape[0]), _ptr(block_table),
                     c_int(block_table.shape[1]), _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(tokens), c_int(seqs),
@@ -491,6 +522,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
             if info is not None:
                 info.update(kernel="mma")
             if max_q_len > 1:
+                _set_bounds("attention_mma", keys)
                 _check(lib, lib.pae_paged_attention_prefill(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
                     _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads),
@@ -503,6 +535,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     if info is not None:
         info.update(kernel="simt")
     lib = _lib("attention_simt")
+    _set_bounds("attention_simt", keys)
     _check(lib, lib.pae_paged_attention_simt(
         _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
         _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads),
