@@ -349,18 +349,26 @@ def near_tie(engine, prompt, first, second, at: int, torch) -> bool:
 
 def stream_7b(torch, layers: int) -> dict:
     """256 seeded requests, prompts U[16, 2048], decodes U[8, 1024], 64 at a time, 8,192 tokens a
-    step, the reference's pool of 3,584 pages (bench/workload.py:241-254)."""
+    step (bench/workload.py:241-254). Twice: with a pool in which 64 requests of the longest kind
+    fit (12,352 pages of 16 tokens, 11.3 GB at this shape), and with the reference's pool of 3,584
+    pages (engine/cache.py:29-35), which 64 such requests overflow, so that many are preempted
+    and recomputed."""
     from paged_attention_engine_b200.cli import synthetic_stream
     from paged_attention_engine_b200.engine.llm import Engine
 
     model = dict(MODEL_7B, num_hidden_layers=layers)
     engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
     stream = synthetic_stream("mixed", 0, 256, model["vocab_size"], smoke=False)
-    info = run_stream(engine, stream, 3584, 64, 8192, torch)
+    roomy_pages = 64 * (3072 // BLOCK_SIZE + 1)
+    info = run_stream(engine, stream, roomy_pages, 64, 8192, torch)
+    tight = run_stream(engine, stream, 3584, 64, 8192, torch)
     out = {
         "stream_7b_tok_s": round(info["tokens_per_s"], 1), "stream_7b_seconds": round(info["seconds"], 2),
         "stream_7b_generated": info["generated"], "stream_7b_steps": info["steps"],
-        "stream_7b_preemptions": info["preemptions"], "stream_7b_weight_gb": round(engine.weight_bytes() / 1e9, 2),
+        "stream_7b_preemptions": info["preemptions"], "stream_7b_pages": roomy_pages,
+        "stream_7b_pool3584_tok_s": round(tight["tokens_per_s"], 1), "stream_7b_pool3584_steps": tight["steps"],
+        "stream_7b_pool3584_preemptions": tight["preemptions"],
+        "stream_7b_weight_gb": round(engine.weight_bytes() / 1e9, 2),
         "stream_7b_layers": layers, "stream_7b_layers_of_config": MODEL_7B["num_hidden_layers"],
     }
     del engine

@@ -23,6 +23,11 @@ class TokenEmbedding(Part):
         super().__init__(spec, tensors, runtime)
         self.weight = tensors[spec.tensor_name("weight")]
 
+    def step_weight_bytes(self, num_tokens: int) -> int:
+        """A step reads one row of the table per token, not the table. (When the head is tied to it,
+        the head reads all of it and counts it.)"""
+        return num_tokens * self.weight.shape[1] * self.weight.element_size()
+
     def forward(self, ctx):
         # A negative id is "the token sampled for this request in the step before" (see
         # StepContext.feedback); the kernel looks it up on the device.
