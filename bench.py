@@ -160,16 +160,16 @@ def decode_bytes(engine, cache, contexts) -> float:
     return float(engine.weight_bytes(len(contexts)) + cache.bytes_per_token() * sum(contexts))
 
 
-def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampling_row, passes: int = PASSES):
+def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampling_row, passes: int = PASSES, context: int = CONTEXT):
     """Device-timed decode: `warmup` steps, then `passes` passes of `steps` steps of `batch`
-    single tokens, the last pass ending at CONTEXT. Returns the passes' ms per step and what
+    single tokens, the last pass ending at `context`. Returns the passes' ms per step and what
     the median pass read."""
     from paged_attention_engine_b200.engine.batch import StepEntry
     from paged_attention_engine_b200.kernels import ops
 
     total = warmup + passes * steps
-    start_context = CONTEXT - total
-    blocks = batch * (CONTEXT // BLOCK_SIZE + 1) + 8
+    start_context = context - total
+    blocks = batch * (context // BLOCK_SIZE + 1) + 8
     cache = engine.new_paged_cache(blocks, BLOCK_SIZE, max(batch, 1))
     for pool in cache.pools:
         pool.normal_(0.0, 0.5)       # what the pages hold does not change a decode step's cost
@@ -362,7 +362,12 @@ def stream_7b(torch, layers: int) -> dict:
     roomy_pages = 64 * (3072 // BLOCK_SIZE + 1)
     info = run_stream(engine, stream, roomy_pages, 64, 8192, torch)
     tight = run_stream(engine, stream, 3584, 64, 8192, torch)
+    from paged_attention_engine_b200.sampling import SamplingRow
+
+    step = time_decode(engine, 64, 24, 8, torch, SamplingRow, passes=PASSES, context=1024)
     out = {
+        "decode_7b_b64_ctx1024": round(step["tokens_per_s"], 1),
+        "decode_7b_b64_ctx1024_hbm_frac": round(step["bytes"] / (step["ms_per_step"] / 1e3) / 1e9 / peaks()["hbm_gbs"], 4),
         "stream_7b_tok_s": round(info["tokens_per_s"], 1), "stream_7b_seconds": round(info["seconds"], 2),
         "stream_7b_generated": info["generated"], "stream_7b_steps": info["steps"],
         "stream_7b_preemptions": info["preemptions"], "stream_7b_pages": roomy_pages,
@@ -400,7 +405,12 @@ def pressure_32b(torch, layers: int) -> dict:
         at = next(k for k in range(min(len(a), len(b))) if a[k] != b[k])
         parted.append(at)
         ties += bool(near_tie(engine, prompt, b, a, at, torch))
+    from paged_attention_engine_b200.sampling import SamplingRow
+
+    step = time_decode(engine, 64, 16, 8, torch, SamplingRow, passes=PASSES, context=1024)
     out = {
+        "decode_32b_b64_ctx1024": round(step["tokens_per_s"], 1),
+        "decode_32b_b64_ctx1024_hbm_frac": round(step["bytes"] / (step["ms_per_step"] / 1e3) / 1e9 / peaks()["hbm_gbs"], 4),
         "pressure_32b_tok_s": round(tight["tokens_per_s"], 1), "pressure_32b_seconds": round(tight["seconds"], 2),
         "pressure_32b_steps": tight["steps"], "pressure_32b_preemptions": tight["preemptions"],
         "pressure_32b_unpressured_tok_s": round(roomy["tokens_per_s"], 1),

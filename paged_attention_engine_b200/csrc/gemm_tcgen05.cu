@@ -23,20 +23,14 @@
 // mbarrier wait is bounded: when one gives up it records a code in `error`, the roles
 // leave their loops, loads in flight are waited for (bounded again), tensor memory is
 // freed and the block returns.
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 using namespace pae;
+using namespace pae_tcgen05;
 
 namespace {
 
 constexpr int BM = 128;          // MMA rows per tile
-constexpr int BK = 64;           // bf16 elements per k-block: one 128-byte swizzle row
-constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int EPILOGUE_SHARES = 2;           // epilogue warps per quarter of the rows (three were measured slower, one much slower)
 constexpr int PERSISTENT_THREADS = 64 + 128 * EPILOGUE_SHARES;     // TMA warp, MMA warp, the epilogue warps
@@ -68,33 +62,6 @@ struct Params {
   int skip_kb;       // self-test of the give-up path only: the k-block (of each block's range) that is never loaded
 };
 
-// ---------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-
 // Waits for a phase of an mbarrier, at most WAIT_LIMIT polls. On giving up it raises the
 // block's abort flag and records `code`; it also returns false as soon as another role
 // has raised the flag.
@@ -108,77 +75,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *abort_flag = 1;
   atomicCAS(error, 0, code);
   return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t columns) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(columns) : "memory");
-}
-
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// D[tmem] (+)= A[smem] . B[smem]^T, both K-major, one thread issues.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
-// 16 consecutive float32 columns of this thread's lane of tensor memory.
-__device__ __forceinline__ void tmem_load16(uint32_t address, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(address)
-      : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128
-// bytes, groups of 8 rows 1024 bytes apart (stride byte offset), leading byte offset 1
-// (unused with a swizzle), descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
-  uint64_t d = 0;
-  d |= (uint64_t)((address & 0x3FFFFu) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// Instruction descriptor: float32 accumulator (bits 4-5 = 1), bfloat16 A and B (bits 7-9
-// and 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
-__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // One thread's 16 consecutive outputs of row `row` from column `col0` on: bias, residual,
@@ -758,63 +654,6 @@ __global__ void __launch_bounds__(PERSISTENT_THREADS) gemm_tcgen05_persistent_ke
 // ---------------------------------------------------------------------------------------
 // Host side: tensor maps (cached by pointer and shape), launch.
 // ---------------------------------------------------------------------------------------
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encode_tiled() {
-  static EncodeTiled fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
-        result != cudaDriverEntryPointSuccess)
-      ptr = nullptr;
-    return (EncodeTiled)ptr;
-  }();
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  int rows, k, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& key) const {
-    size_t h = (size_t)key.ptr;
-    h = h * 1000003u ^ (size_t)key.rows;
-    h = h * 1000003u ^ (size_t)key.k;
-    return h * 1000003u ^ (size_t)key.box_rows;
-  }
-};
-
-// A [rows, k] bfloat16 row-major matrix as boxes of 64 elements x box_rows rows, 128-byte
-// swizzle, zero fill outside the matrix.
-int tensor_map(CUtensorMap* out, const void* ptr, int rows, int k, int box_rows) {
-  static std::mutex mutex;
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  std::lock_guard<std::mutex> guard(mutex);
-  const MapKey key{ptr, rows, k, box_rows};
-  auto found = cache.find(key);
-  if (found != cache.end()) {
-    *out = found->second;
-    return 0;
-  }
-  EncodeTiled encode = encode_tiled();
-  if (encode == nullptr) return fail(101, "linear_tcgen05: the driver does not export cuTensorMapEncodeTiled");
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t element_strides[2] = {1, 1};
-  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, element_strides,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(102, "linear_tcgen05: cuTensorMapEncodeTiled failed with %d for [%d, %d]", (int)r, rows, k);
-  if (cache.size() > 4096) cache.clear();
-  cache.emplace(key, *out);
-  return 0;
-}
-
 template <int BN, int MODE, bool SELFTEST = false>
 int launch(const Params& p, const void* a, const void* b, int k, int splits, cudaStream_t stream) {
   using T = Tile<BN>;

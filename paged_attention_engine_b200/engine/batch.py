@@ -147,6 +147,7 @@ class BatchBuilder:
         table_width: int | None = None,
         into: torch.Tensor | None = None,
         pad_to: int | None = None,
+        max_kv_len: int | None = None,
     ) -> StepContext:
         """Flattens the entries. `sampling` (one row per wanted place: temperature, seed,
         request key, output index) travels in the same copy. `table_width` fixes the width of
@@ -155,7 +156,9 @@ class BatchBuilder:
         all their logits only) adds rows up to that many entries: each is a token at position 0
         of nobody's request, which writes no page (slot -1), reads page 0 and owns the spare
         state slot behind the real ones; its logits and its token are computed and ignored, so
-        that steps of neighbouring batch sizes can share one captured graph."""
+        that steps of neighbouring batch sizes can share one captured graph. `max_kv_len` is the
+        longest context that the step's kernels are to plan for (at least the true one; a captured
+        graph fixes it); without it, the table's width when that is fixed, else the true one."""
         if not entries:
             raise ValueError("a step needs at least one entry")
         manager = self.manager
@@ -221,6 +224,9 @@ class BatchBuilder:
             if table_width < width:
                 raise ValueError(f"block tables of {width} pages do not fit the fixed width {table_width}")
             width = table_width
+        planned_kv = max_kv_len if max_kv_len is not None else (width * page if table_width is not None else max_kv)
+        if planned_kv < max_kv:
+            raise ValueError(f"a context of {max_kv} keys does not fit the {planned_kv} that the step plans for")
         num_groups = len(manager.groups)
         if sampling is not None and len(sampling) != len(rows) - pads:
             raise ValueError(f"{len(sampling)} sampling rows for {len(rows) - pads} wanted places")
@@ -285,7 +291,7 @@ class BatchBuilder:
             ops=self.ops, dtype=self.dtype, device=self.device, num_tokens=total, num_seqs=b,
             token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
             kv_len=part(5), state_slot=part(6), logit_rows=part(7),
-            max_q_len=max(q_lens), max_kv_len=width * page if table_width is not None else max_kv,
+            max_q_len=max(q_lens), max_kv_len=planned_kv,
             num_single=sum(1 for n in q_lens if n == 1), wants_every_token=len(rows) == total and rows == list(range(total)), groups=groups,
             host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
             sampling=sampling_parts, buffer=dev,

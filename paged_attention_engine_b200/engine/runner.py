@@ -48,9 +48,14 @@ class _DecodeGraph:
 
 
 class ModelRunner:
-    # A graph per (batch size, block-table width, sampling). They share one memory pool (they never
-    # run at the same time), so a graph costs its launches and little else.
+    # A graph per (batch size, block-table width, longest context rounded up, sampling). They share
+    # one memory pool (they never run at the same time), so a graph costs its launches and little else.
     MAX_GRAPHS = 512
+    # A recorded step plans its attention (how the keys are sliced) for a longest context that is
+    # fixed in the recording: the true longest context rounded up to a multiple of this many
+    # keys, not to the block table's width, which is a power of two (at context 4,097 the table
+    # is 8,192 keys wide, and slices planned for 8,192 keys would be twice as long as needed).
+    KV_BUCKET = 512
 
     def __init__(self, model: DecoderModel, cache: PagedKVCache, use_graphs: bool = True) -> None:
         self.model = model
@@ -64,7 +69,7 @@ class ModelRunner:
         # The checked build hands its limits to the libraries between launches: it records no graphs.
         self.use_graphs = (use_graphs and self.runtime.device.type == "cuda" and model.graph_safe
                            and not getattr(self.runtime.ops, "bounds_checked", False))
-        self.graphs: dict[tuple[int, int, bool], _DecodeGraph] = {}
+        self.graphs: dict[tuple[int, int, int, bool], _DecodeGraph] = {}
         self.graph_pool = None
         self.capture_stream = None
         self.graph_replays = 0
@@ -95,7 +100,7 @@ class ModelRunner:
             ops.scatter_tokens(self.last_token, tokens, ctx.logit_rows, ctx.seq_index, ctx.state_slot)
         return logits, tokens
 
-    def _graph_key(self, entries, sampling) -> tuple[int, int, bool] | None:
+    def _graph_key(self, entries, sampling) -> tuple[int, int, int, bool] | None:
         if not self.use_graphs or len(entries) > 256:
             return None
         for e in entries:
@@ -106,7 +111,8 @@ class ModelRunner:
         width = 16
         while width * page < longest:
             width *= 2
-        return (self.graph_batch(len(entries)), width, sampling is not None)
+        bucket = min(width * page, -(-longest // self.KV_BUCKET) * self.KV_BUCKET)
+        return (self.graph_batch(len(entries)), width, bucket, sampling is not None)
 
     @staticmethod
     def graph_batch(count: int) -> int:
@@ -123,7 +129,7 @@ class ModelRunner:
         key = self._graph_key(entries, sampling)
         slot = self.graphs.get(key) if key is not None else None
         if slot is not None and slot.graph is not None:
-            self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer, pad_to=key[0])
+            self.builder.build(entries, sampling, table_width=key[1], into=slot.buffer, pad_to=key[0], max_kv_len=key[2])
             slot.graph.replay()
             self.model.forward_pass_count += 1
             self.graph_replays += 1
@@ -135,7 +141,7 @@ class ModelRunner:
         elif key is not None and len(self.graphs) < self.MAX_GRAPHS:
             # First time for this shape: its launches are recorded (nothing runs), then the
             # recording is replayed, which is this step's real work.
-            ctx = self.builder.build(entries, sampling, table_width=key[1], pad_to=key[0])
+            ctx = self.builder.build(entries, sampling, table_width=key[1], pad_to=key[0], max_kv_len=key[2])
             slot = _DecodeGraph(ctx.buffer)
             self._capture(slot, ctx)
             self.graphs[key] = slot
