@@ -221,21 +221,21 @@ def time_decode(engine, batch: int, steps: int, warmup: int, torch, sampling_row
     return info
 
 
-def time_prefill(engine, torch, repeats: int = PASSES):
+def time_prefill(engine, torch, repeats: int = PASSES, tokens: int = PREFILL_TOKENS):
     from paged_attention_engine_b200.engine.batch import StepEntry
 
-    cache = engine.new_paged_cache(PREFILL_TOKENS // BLOCK_SIZE + 2, BLOCK_SIZE, 2)
+    cache = engine.new_paged_cache(tokens // BLOCK_SIZE + 2, BLOCK_SIZE, 2)
     runner = engine.new_runner(cache)
     gen = torch.Generator().manual_seed(99)
     times = []
     for r in range(repeats + 2):
-        ids = torch.randint(0, engine.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+        ids = torch.randint(0, engine.vocab_size, (tokens,), generator=gen).tolist()
         runner.begin_request("prefill")
-        assert cache.manager.reserve("prefill", PREFILL_TOKENS).ok
+        assert cache.manager.reserve("prefill", tokens).ok
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        runner.step([StepEntry("prefill", ids, (PREFILL_TOKENS - 1,))])
+        runner.step([StepEntry("prefill", ids, (tokens - 1,))])
         end.record()
         torch.cuda.synchronize()
         if r >= 2:
@@ -561,6 +561,10 @@ def main() -> int:
     parser.add_argument("--skip-streams", action="store_true", help="leave out the 7B stream and the 32B pressure run")
     parser.add_argument("--layers-7b", type=int, default=MODEL_7B["num_hidden_layers"])
     parser.add_argument("--layers-32b", type=int, default=MODEL_32B["num_hidden_layers"])
+    parser.add_argument("--shape", choices=("1.5b", "7b", "32b"), default="1.5b",
+                        help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
+    parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
     parser.add_argument("--only", choices=("all", "decode", "prefill", "stream7b", "pressure32b"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
@@ -591,20 +595,26 @@ def main() -> int:
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
         return 0
 
-    model = dict(MODEL)
+    model = dict({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape] if args.only != "all" else MODEL)
+    if args.only != "all" and args.shape != "1.5b" and args.layers == MODEL["num_hidden_layers"]:
+        args.layers = model["num_hidden_layers"]
     model["num_hidden_layers"] = args.layers
     engine = Engine.from_random(model, seed=0, dtype="bfloat16", device="cuda:0")
 
     if args.only == "prefill":
-        prefill = time_prefill(engine, torch)
-        flops = prefill_flops(model, PREFILL_TOKENS)
-        print(json.dumps({"only": "prefill", "ms": round(prefill["median"], 3), "tokens": PREFILL_TOKENS,
+        prefill = time_prefill(engine, torch, tokens=args.tokens)
+        flops = prefill_flops(model, args.tokens)
+        print(json.dumps({"only": "prefill", "shape": args.shape, "layers": args.layers, "ms": round(prefill["median"], 3),
+                          "tokens": args.tokens, "tflops": round(flops / (prefill["median"] / 1e3) / 1e12, 1),
                           "frac": round(flops / (prefill["median"] / 1e3) / (peak["bf16_tflops"] * 1e12), 4)}))
         return 0
     if args.only == "decode":
-        decode = time_decode(engine, args.batch, args.steps, warmup, torch, SamplingRow)
-        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": round(decode["ms_per_step"], 4),
-                          "tokens_per_s": round(decode["tokens_per_s"], 1), "launches": decode["launches"]}))
+        decode = time_decode(engine, args.batch, args.steps, warmup, torch, SamplingRow, context=args.context)
+        gbs = decode["bytes"] / (decode["ms_per_step"] / 1e3) / 1e9
+        print(json.dumps({"only": "decode", "shape": args.shape, "layers": args.layers, "batch": args.batch,
+                          "context": args.context, "ms_per_step": round(decode["ms_per_step"], 4),
+                          "tokens_per_s": round(decode["tokens_per_s"], 1), "gb_per_step": round(decode["bytes"] / 1e9, 3),
+                          "hbm_frac": round(gbs / peak["hbm_gbs"], 4), "launches": decode["launches"]}))
         return 0
 
     sampler = ClockSampler()

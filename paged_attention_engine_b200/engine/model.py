@@ -10,12 +10,19 @@ batched step from a loop over requests.
 
 from __future__ import annotations
 
+import os
 from typing import Any
 
 import torch
 
 from ..config.model_spec import ModelSpec
 from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, REGISTRIES, Runtime, layer_part_specs
+
+
+# PAE_NVTX=1 marks every step's traversal and every schedule entry with an NVTX range, for a
+# timeline profiler (the reference has no tracing at all; its stand-ins, the pass counter and the
+# scheduler's event log, are kept as well).
+NVTX = os.environ.get("PAE_NVTX", "0") not in ("", "0")
 
 
 class Layer:
@@ -58,10 +65,18 @@ class DecoderModel:
         """Runs the step's tokens through every schedule entry; float32 logits
         [wanted, vocab] at `ctx.logit_rows`, or None when nothing is wanted."""
         self.forward_pass_count += 1
+        if NVTX:
+            torch.cuda.nvtx.range_push(f"traversal: {ctx.num_tokens} tokens of {ctx.num_seqs} requests")
         hidden = self.embedding.forward(ctx)
         for position, entry in enumerate(self.spec.schedule):
             layer = self.layers[entry.layer]
+            if NVTX:
+                torch.cuda.nvtx.range_push(f"entry {position}: layer {entry.layer}")
             hidden = layer.block.forward(ctx, hidden, layer, entry_caches[position])
+            if NVTX:
+                torch.cuda.nvtx.range_pop()
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
         if ctx.logit_rows.numel() == 0:
             return None
         # A step that wants the logits of all its tokens (decoding) needs no gather, and the final

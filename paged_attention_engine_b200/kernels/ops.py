@@ -12,6 +12,7 @@ norm weights float32, indices int32, logits float32.
 from __future__ import annotations
 
 import ctypes
+import re
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -59,6 +60,36 @@ def require_cuda() -> None:
         )
 
 
+_SIGNATURE = re.compile(r"PAE_EXPORT\s+([\w\s\*]+?)\s*\b(pae_\w+)\s*\(([^)]*)\)")
+
+
+def _ctype_of(declaration: str):
+    if "*" in declaration:
+        return ctypes.c_char_p if declaration.strip().startswith("const char") and declaration.strip().endswith("*") else c_void_p
+    if "long long" in declaration:
+        return ctypes.c_longlong
+    if "float" in declaration:
+        return c_float
+    return c_int
+
+
+def _declare_signatures(lib: ctypes.CDLL, name: str) -> None:
+    """Tells ctypes the argument and result types of the family's entry points, read from their
+    declarations in the sources (`PAE_EXPORT <type> pae_name(<arguments>)`): a call then takes plain
+    Python integers, floats and addresses, which is quicker than wrapping each in a ctypes object,
+    and an address is never cut to 32 bits."""
+    for source in build.FAMILIES[name]:
+        text = (build.CSRC / source).read_text()
+        for result, function, arguments in _SIGNATURE.findall(text):
+            entry = getattr(lib, function, None)
+            if entry is None:
+                continue
+            arguments = arguments.strip()
+            entry.argtypes = [] if arguments in ("", "void") else [
+                c_void_p if "*" in a else _ctype_of(a) for a in arguments.split(",")]
+            entry.restype = _ctype_of(result)
+
+
 def _lib(name: str) -> ctypes.CDLL:
     lib = _libs.get(name)
     if lib is None:
@@ -69,10 +100,7 @@ def _lib(name: str) -> ctypes.CDLL:
         except OSError as exc:
             raise KernelError(f"cannot load {path}: {exc}") from exc
         lib.pae_last_error.restype = ctypes.c_char_p
-        if name == "attention_mma":
-            lib.pae_decode_scratch_floats.restype = ctypes.c_longlong
-        if name == "sampling":
-            lib.pae_sample_scratch_words.restype = ctypes.c_longlong
+        _declare_signatures(lib, name)
         _libs[name] = lib
     return lib
 
@@ -93,7 +121,8 @@ def _check(lib: ctypes.CDLL, code: int, count: int = 1) -> None:
 
 
 def _ptr(t: torch.Tensor | None):
-    return None if t is None else c_void_p(t.data_ptr())
+    """A tensor's address as an integer (the entry points' pointer arguments are declared)."""
+    return None if t is None else t.data_ptr()
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -105,8 +134,8 @@ _get_device = getattr(torch._C, "_cuda_getDevice", None)
 def _stream():
     """The current stream's handle (asked for at every launch: the quick way when torch has it)."""
     if _raw_stream is not None and _get_device is not None:
-        return c_void_p(_raw_stream(_get_device()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _raw_stream(_get_device())
+    return torch.cuda.current_stream().cuda_stream
 
 
 def _code(t: torch.Tensor) -> int:
@@ -159,8 +188,8 @@ def materialized(x):
         splits, m, n = x.partial.shape
         out = torch.empty((m, n), dtype=x.dtype, device=x.partial.device)
         lib = _lib("gemm_tcgen05")
-        _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(x.partial), _ptr(x.bias), _ptr(x.residual), c_int(splits),
-                                          c_int(m), c_int(n), c_int(1 if x.dtype == torch.float32 else 0), _stream()))
+        _check(lib, lib.pae_reduce_splits(_ptr(out), _ptr(x.partial), _ptr(x.bias), _ptr(x.residual), splits,
+                                          m, n, (1 if x.dtype == torch.float32 else 0), _stream()))
         x.value = out
     return x.value
 
@@ -171,8 +200,8 @@ def gather_rows(x, rows: torch.Tensor) -> torch.Tensor:
     _need(rows, "gather_rows: rows", torch.int32)
     out = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
     lib = _lib("elementwise")
-    _check(lib, lib.pae_gather_rows(_ptr(out), _ptr(x), _ptr(rows), c_int(rows.numel()), c_int(x.shape[0]),
-                                    c_int(x.shape[1]), c_int(_code(x)), _stream()))
+    _check(lib, lib.pae_gather_rows(_ptr(out), _ptr(x), _ptr(rows), (rows.numel()), x.shape[0],
+                                    x.shape[1], (_code(x)), _stream()))
     return out
 
 
@@ -189,8 +218,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, feedback=None) -> torch.Te
     out = torch.empty((ids.numel(), table.shape[1]), dtype=table.dtype, device=table.device)
     lib = _lib("elementwise")
     _check(lib, lib.pae_embedding_feedback(_ptr(out), _ptr(table), _ptr(ids), _ptr(last_token), _ptr(state_slot),
-                                           _ptr(seq_index), c_int(ids.numel()), c_int(table.shape[0]),
-                                           c_int(table.shape[1]), c_int(_code(table)), _stream()))
+                                           _ptr(seq_index), (ids.numel()), table.shape[0],
+                                           table.shape[1], (_code(table)), _stream()))
     return out
 
 
@@ -202,7 +231,7 @@ def scatter_tokens(last_token, tokens, logit_rows, seq_index, state_slot) -> Non
         _need(t, f"scatter_tokens: {name}", torch.int32)
     lib = _lib("elementwise")
     _check(lib, lib.pae_scatter_tokens(_ptr(last_token), _ptr(tokens), _ptr(logit_rows), _ptr(seq_index),
-                                       _ptr(state_slot), c_int(tokens.numel()), _stream()))
+                                       _ptr(state_slot), (tokens.numel()), _stream()))
 
 
 def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -214,9 +243,9 @@ def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
         value = torch.empty((m, n), dtype=x.dtype, device=x.device)
         normed = torch.empty_like(value)
         lib = _lib("fused_decode")
-        _check(lib, lib.pae_splitk_rms_norm(_ptr(normed), _ptr(value), _ptr(x.partial), c_int(splits), _ptr(x.bias),
-                                            _ptr(x.residual), _ptr(weight), c_int(m), c_int(n), c_float(eps),
-                                            c_int(_DTYPE_CODE[x.dtype]), _stream()))
+        _check(lib, lib.pae_splitk_rms_norm(_ptr(normed), _ptr(value), _ptr(x.partial), splits, _ptr(x.bias),
+                                            _ptr(x.residual), _ptr(weight), m, n, eps,
+                                            _DTYPE_CODE[x.dtype], _stream()))
         x.value = value
         return normed
     x = materialized(x)
@@ -224,8 +253,8 @@ def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
     out = torch.empty_like(x)
     lib = _lib("elementwise")
     rows = x.numel() // x.shape[-1] if x.numel() else 0
-    _check(lib, lib.pae_rms_norm(_ptr(out), _ptr(x), _ptr(weight), c_int(rows), c_int(x.shape[-1]), c_float(eps),
-                                 c_int(_code(x)), _stream()))
+    _check(lib, lib.pae_rms_norm(_ptr(out), _ptr(x), _ptr(weight), rows, (x.shape[-1]), eps,
+                                 (_code(x)), _stream()))
     return out
 
 
@@ -311,8 +340,8 @@ def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
         return _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     lib = _lib("gemm_simt")
-    _check(lib, lib.pae_linear_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
-                                    c_int(k), c_int(_code(x)), c_int(_code(weight)), c_int(_DTYPE_CODE[out_dtype]),
+    _check(lib, lib.pae_linear_simt(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), m, n,
+                                    k, (_code(x)), (_code(weight)), _DTYPE_CODE[out_dtype],
                                     _stream()))
     return out
 
@@ -320,30 +349,30 @@ def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
 def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch.Tensor:
     lib = _lib("gemm_tcgen05")
     flag = _error_flag(x.device)
-    out_f32 = c_int(1 if out_dtype == torch.float32 else 0)
+    out_f32 = (1 if out_dtype == torch.float32 else 0)
     if m <= SWAPPED_MAX_TOKENS:
         # Few tokens: weight rows fill the MMA's 128 rows, K is split, partial sums are
         # float32 scratch that the reduction (or nothing, for one split) turns into the output.
-        splits = lib.pae_linear_swapped_splits(c_int(n), c_int(k))
+        splits = lib.pae_linear_swapped_splits(n, k)
         partial = torch.empty((splits, m, n), dtype=torch.float32, device=x.device)
-        _check(lib, lib.pae_linear_tcgen05_swapped(_ptr(partial), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
+        _check(lib, lib.pae_linear_tcgen05_swapped(_ptr(partial), _ptr(x), _ptr(weight), m, n, k,
                                                    _ptr(flag), _stream()))
         if splits == 1 and bias is None and residual is None and out_dtype == torch.float32:
             return partial[0]
         pending = PendingSum(partial, bias, residual, out_dtype)
         return pending if fuse_split_sums else materialized(pending)
-    planes = lib.pae_linear_tcgen05_plane_count(c_int(m), c_int(n), c_int(k))
+    planes = lib.pae_linear_tcgen05_plane_count(m, n, k)
     if planes > 1:
         # Few output tiles and a long K (a down projection for a few hundred tokens): each
         # tile's K is shared out over several blocks, whose float32 planes are added up later.
         partial = torch.empty((planes, m, n), dtype=torch.float32, device=x.device)
-        _check(lib, lib.pae_linear_tcgen05_planes(_ptr(partial), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
-                                                  c_int(planes), _ptr(flag), _stream()))
+        _check(lib, lib.pae_linear_tcgen05_planes(_ptr(partial), _ptr(x), _ptr(weight), m, n, k,
+                                                  planes, _ptr(flag), _stream()))
         pending = PendingSum(partial, bias, residual, out_dtype)
         return pending if fuse_split_sums else materialized(pending)
     out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-    _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), c_int(m), c_int(n),
-                                       c_int(k), out_f32, _ptr(flag), _stream()))
+    _check(lib, lib.pae_linear_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(residual), m, n,
+                                       k, out_f32, _ptr(flag), _stream()))
     return out
 
 
@@ -353,8 +382,8 @@ def rotary_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tenso
     half = inv_freq.numel()
     table = torch.empty((positions.numel(), 2 * half), dtype=torch.float32, device=positions.device)
     lib = _lib("elementwise")
-    _check(lib, lib.pae_rotary_table(_ptr(table), _ptr(positions), _ptr(inv_freq), c_int(positions.numel()),
-                                     c_int(half), _stream()))
+    _check(lib, lib.pae_rotary_table(_ptr(table), _ptr(positions), _ptr(inv_freq), (positions.numel()),
+                                     half, _stream()))
     return table
 
 
@@ -381,9 +410,9 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
         lib = _lib("fused_decode")
         _set_bounds("fused_decode", keys if slots is not None else None)
         _check(lib, lib.pae_splitk_rotary_cache_write(
-            _ptr(out), _ptr(qkv.partial), c_int(splits), _ptr(qkv.bias), _ptr(table), _ptr(slots), key_ptr, value_ptr,
-            c_int(tokens), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
-            c_int(_DTYPE_CODE[qkv.dtype]), _stream()))
+            _ptr(out), _ptr(qkv.partial), splits, _ptr(qkv.bias), _ptr(table), _ptr(slots), key_ptr, value_ptr,
+            tokens, num_heads, num_kv_heads, head_dim, page_size,
+            _DTYPE_CODE[qkv.dtype], _stream()))
         qkv.value = out
         return out
     qkv = materialized(qkv)
@@ -391,8 +420,8 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
     lib = _lib("elementwise")
     _set_bounds("elementwise", keys if slots is not None else None)
     _check(lib, lib.pae_rotary_qk_cache_write(
-        _ptr(qkv), _ptr(table), _ptr(slots), key_ptr, value_ptr, c_int(tokens), c_int(num_heads), c_int(num_kv_heads),
-        c_int(head_dim), c_int(page_size), c_int(_code(qkv)), _stream()))
+        _ptr(qkv), _ptr(table), _ptr(slots), key_ptr, value_ptr, tokens, num_heads, num_kv_heads,
+        head_dim, page_size, (_code(qkv)), _stream()))
     return qkv
 
 
@@ -411,7 +440,7 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
             and weight.shape[1] == k and not isinstance(x, PendingSum) and _tensor_core_shape(x, weight, None, x.dtype)
             and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
         lib = _lib("gemm_tcgen05")
-        if lib.pae_linear_rotary_tcgen05_supports(c_int(head_dim)):
+        if lib.pae_linear_rotary_tcgen05_supports(head_dim):
             _need(x, "qkv_projection: x")
             _need(weight, "qkv_projection: weight")
             if bias is not None:
@@ -430,8 +459,8 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
             _set_bounds("gemm_tcgen05", keys if slots is not None else None)
             _check(lib, lib.pae_linear_rotary_tcgen05(
                 _ptr(out), _ptr(x), _ptr(weight), _ptr(bias), _ptr(table), _ptr(slots),
-                _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), c_int(m),
-                c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(k),
+                _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), m,
+                num_heads, num_kv_heads, head_dim, page_size, k,
                 _ptr(_error_flag(x.device)), _stream()))
             return out
     return rotary_qk_cache_write(linear(x, weight, bias), table, slots, keys, values, num_heads, num_kv_heads, head_dim,
@@ -461,17 +490,17 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
                       num_kv_heads, head_dim, page_size, max_kv_len, scale, window) -> None:
     """The requests that bring one token: sliced over their keys, then merged."""
     count = seqs if singles < 0 else singles
-    wave = lib.pae_decode_blocks_per_wave(c_int(head_dim))
+    wave = lib.pae_decode_blocks_per_wave(head_dim)
     slice_keys, max_slices = decode_slicing(count, num_kv_heads, max_kv_len, wave_blocks=wave,
                                             slices_per_block=lib.pae_decode_slices_per_block())
-    floats = lib.pae_decode_scratch_floats(c_int(seqs), c_int(num_heads), c_int(head_dim), c_int(max_slices))
+    floats = lib.pae_decode_scratch_floats(seqs, num_heads, head_dim, max_slices)
     scratch = torch.empty(floats, dtype=torch.float32, device=qkv.device)
     launches = 2
     _set_bounds("attention_mma", keys)
     _check(lib, lib.pae_paged_attention_decode(
-        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
-        _ptr(q_start), _ptr(kv_len), c_int(seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_float(scale), c_int(window), c_int(slice_keys), c_int(max_slices),
+        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1],
+        _ptr(q_start), _ptr(kv_len), seqs, num_heads, num_kv_heads, head_dim,
+        page_size, scale, window, slice_keys, max_slices,
         _ptr(scratch), _stream()), launches)
 
 
@@ -497,20 +526,20 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     out = torch.empty((tokens, num_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     if qkv.dtype == torch.bfloat16 and use_tensor_cores:
         lib = _lib("attention_mma")
-        mma_ok = bool(lib.pae_attention_mma_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)))
+        mma_ok = bool(lib.pae_attention_mma_supports(num_heads, num_kv_heads, head_dim, page_size))
         singles = num_single if num_single is not None else (seqs if max_q_len == 1 else -1)
         # Portions of 64 tokens and more: both products on tcgen05, one thread per query row.
         if use_tcgen05_attention and max_q_len >= TCGEN05_ATTENTION_MIN_TOKENS:
             tc5 = _lib("attention_tcgen05")
-            if tc5.pae_attention_tcgen05_supports(c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size)):
+            if tc5.pae_attention_tcgen05_supports(num_heads, num_kv_heads, head_dim, page_size):
                 decode_after = mma_ok and singles != 0
                 chosen = c_int(-1)
                 _set_bounds("attention_tcgen05", keys)
                 _check(tc5, tc5.pae_paged_attention_prefill_tcgen05(
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), ctypes.c_longlong(keys.shape[0]), _ptr(block_table),
-                    c_int(block_table.shape[1]), _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(tokens), c_int(seqs),
-                    c_int(max_q_len), c_int(max_kv_len), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
-                    c_float(scale), c_int(window), c_int(1 if decode_after else 0), c_int(singles), c_int(form),
+                    block_table.shape[1], _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), tokens, seqs,
+                    max_q_len, max_kv_len, num_heads, num_kv_heads, head_dim, page_size,
+                    scale, window, (1 if decode_after else 0), singles, form,
                     ctypes.byref(chosen), _ptr(_error_flag(qkv.device)), _stream()))
                 if info is not None:
                     info.update(kernel="tcgen05", cluster=chosen.value)
@@ -524,10 +553,10 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
             if max_q_len > 1:
                 _set_bounds("attention_mma", keys)
                 _check(lib, lib.pae_paged_attention_prefill(
-                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]),
-                    _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads),
-                    c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_float(scale), c_int(window),
-                    c_int(1), _stream()))
+                    _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1],
+                    _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), seqs, max_q_len, num_heads,
+                    num_kv_heads, head_dim, page_size, scale, window,
+                    1, _stream()))
             if singles != 0:
                 _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
                                   num_kv_heads, head_dim, page_size, max_kv_len, scale, window)
@@ -537,9 +566,9 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
     lib = _lib("attention_simt")
     _set_bounds("attention_simt", keys)
     _check(lib, lib.pae_paged_attention_simt(
-        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
-        _ptr(q_pos0), _ptr(kv_len), c_int(seqs), c_int(max_q_len), c_int(num_heads), c_int(num_kv_heads),
-        c_int(head_dim), c_int(page_size), c_float(scale), c_int(window), c_int(_code(qkv)), _stream()))
+        _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1], _ptr(q_start),
+        _ptr(q_pos0), _ptr(kv_len), seqs, max_q_len, num_heads, num_kv_heads,
+        head_dim, page_size, scale, window, (_code(qkv)), _stream()))
     return out
 
 
@@ -553,15 +582,15 @@ def silu_mul(gate_up, block: int = 0) -> torch.Tensor:
         splits = gate_up.partial.shape[0]
         out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
         lib = _lib("fused_decode")
-        _check(lib, lib.pae_splitk_silu_mul(_ptr(out), _ptr(gate_up.partial), c_int(splits), c_int(tokens),
-                                            c_int(two_i // 2), c_int(block), c_int(_DTYPE_CODE[gate_up.dtype]), _stream()))
+        _check(lib, lib.pae_splitk_silu_mul(_ptr(out), _ptr(gate_up.partial), splits, tokens,
+                                            (two_i // 2), block, _DTYPE_CODE[gate_up.dtype], _stream()))
         return out
     gate_up = materialized(gate_up)
     _need(gate_up, "silu_mul: gate_up")
     out = torch.empty((tokens, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     lib = _lib("elementwise")
-    _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), c_int(tokens), c_int(two_i // 2), c_int(block),
-                                 c_int(_code(gate_up)), _stream()))
+    _check(lib, lib.pae_silu_mul(_ptr(out), _ptr(gate_up), tokens, (two_i // 2), block,
+                                 (_code(gate_up)), _stream()))
     return out
 
 
@@ -593,7 +622,7 @@ def linear_swiglu(x, weight) -> torch.Tensor:
         _need(weight, "linear_swiglu: weight")
         out = torch.empty((m, n // 2), dtype=x.dtype, device=x.device)
         lib = _lib("gemm_tcgen05")
-        _check(lib, lib.pae_linear_swiglu_tcgen05(_ptr(out), _ptr(x), _ptr(weight), c_int(m), c_int(n), c_int(k),
+        _check(lib, lib.pae_linear_swiglu_tcgen05(_ptr(out), _ptr(x), _ptr(weight), m, n, k,
                                                   _ptr(_error_flag(x.device)), _stream()))
         return out
     return silu_mul(linear(x, weight), SWIGLU_BLOCK)
@@ -608,9 +637,9 @@ def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> 
     rows, vocab = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     lib = _lib("sampling")
-    words = lib.pae_sample_scratch_words(c_int(rows), c_int(vocab))
+    words = lib.pae_sample_scratch_words(rows, vocab)
     scratch = torch.empty(words, dtype=torch.int32, device=logits.device) if words else None
     _check(lib, lib.pae_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
-                               _ptr(request_key), _ptr(output_index), c_int(rows), c_int(vocab), _ptr(scratch),
+                               _ptr(request_key), _ptr(output_index), rows, vocab, _ptr(scratch),
                                _stream()), 2 if words else 1)
     return out

@@ -14,6 +14,9 @@ a change to any file of the package.
     factor, for a chosen part of the frequencies only (the rest are not rotated). The
     package's attention part uses it through the same `table(ctx)` as its own.
 
+  * `decayed_sum` is a second mixer with state, written so that a step depends on the batch only
+    through device tensors (it finds its requests' slots in `ctx.state_slot`): a model that holds
+    it keeps its decode steps as recorded CUDA graphs, and replayed steps give the bits of eager ones.
   * `sandwich_norm` is another arrangement of a layer: a norm before AND after each branch
     (four norms, with roles of its own names). The block kind declares its parts; the
     loader, the random weights, the cache plan and the model follow that declaration.
@@ -420,3 +423,119 @@ def test_a_block_kind_declares_its_own_parts():
         gap = (got[key] - want).abs().max().item()
         assert gap <= helpers.tolerance(torch.float32, want), f"{key}: {gap}"
     assert cache.manager.allocators[0].num_free == 24
+
+
+def _register_decayed_sum():
+    from paged_attention_engine_b200.parts import MIXERS, Part, StateNeed
+
+    if "decayed_sum" in MIXERS.names():
+        return
+
+    @MIXERS.register("decayed_sum")
+    class DecayedSum(Part):
+        """out[t] = residual[t] + s[t] with s[t] = decay * s[t - 1] + x[t] per request; the state is
+        s after the request's last token. params: hidden_size, decay. No tensors, no pages.
+        Every index it uses is a device tensor of the step, so its steps can be recorded."""
+
+        graph_safe = True
+
+        @classmethod
+        def state_need(cls, spec):
+            return StateNeed((int(spec.params["hidden_size"]),), torch.float32)
+
+        def __init__(self, spec, tensors, runtime):
+            super().__init__(spec, tensors, runtime)
+            self.decay = float(spec.params["decay"])
+
+        def forward(self, ctx, x, residual, cache):
+            slots = ctx.state_slot.long()[ctx.seq_index.long()]          # [tokens]: each token's state slot
+            rows = x.float()
+            if ctx.max_q_len == 1:                                        # single tokens: one update each, on the device
+                state = cache.state[slots] * self.decay + rows
+                cache.state.index_copy_(0, slots, state)
+                return residual + state.to(residual.dtype)
+            out = residual.clone()                                        # portions: token by token within a request
+            at = 0
+            for slot, count in zip(ctx.host_state_slots, ctx.host_q_lens):
+                state = cache.state[slot]
+                for i in range(count):
+                    state = state * self.decay + rows[at + i]
+                    out[at + i] += state.to(out.dtype)
+                cache.state[slot] = state
+                at += count
+            return out
+
+
+def test_a_stateful_mixer_whose_decode_steps_are_recorded():
+    """State of fixed size per request does not cost the model its CUDA graphs when the mixer reads
+    the step through device tensors only: decode steps are replayed from recordings (padding rows
+    use the spare state slot), and give the same bits as without graphs; the state is zero for a
+    new request and follows the request over portions and single tokens."""
+    from paged_attention_engine_b200.config import ModelSpec, PartSpec, ScheduleEntry
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+    from paged_attention_engine_b200.kernels import ops
+    from paged_attention_engine_b200.parts import Runtime
+    from paged_attention_engine_b200.weights import collect_tensor_specs, place_tensors
+    from paged_attention_engine_b200.weights.random_init import draw
+    from plain import qwen2_plain as plain
+
+    _register_decayed_sum()
+    hidden, vocab, decay = 64, 83, 0.75
+
+    def norm(prefix):
+        return PartSpec("rms_norm", {"size": hidden, "eps": 1e-5}, prefix)
+
+    layers = tuple(
+        helpers.decoder_layer(norm(f"l{i}.n1"), PartSpec("decayed_sum", {"hidden_size": hidden, "decay": decay}), norm(f"l{i}.n2"),
+                              PartSpec("swiglu", {"hidden_size": hidden, "intermediate_size": 48}, f"l{i}.ff"))
+        for i in range(2))
+    spec = ModelSpec("toy_decayed", vocab, hidden, 256, PartSpec("token_embedding", {"vocab_size": vocab, "hidden_size": hidden}, "emb"),
+                     layers, (ScheduleEntry(0), ScheduleEntry(1)), norm("final"),
+                     PartSpec("lm_head", {"vocab_size": vocab, "hidden_size": hidden, "tied_to": "emb.weight"}, "head"))
+    gen = torch.Generator().manual_seed(31)
+    raw = {name: draw(t, gen) for name, t in sorted(collect_tensor_specs(spec).items())}
+    runtime = Runtime(ops, torch.float32, torch.device("cuda:0"))
+    engine = Engine(None, spec, place_tensors(dict(raw), spec, torch.float32, runtime.device), runtime)
+    assert engine.model.graph_safe and not engine.cache_plan.groups and len(engine.cache_plan.state_needs) == 2
+    requests = {"a": helpers.random_tokens(vocab, 19, 41), "b": helpers.random_tokens(vocab, 12, 42), "c": helpers.random_tokens(vocab, 27, 43)}
+
+    def run(use_graphs):
+        cache = engine.new_paged_cache(num_blocks=8, block_size=8, max_num_seqs=4)
+        runner = engine.new_runner(cache, use_graphs=use_graphs)
+        rows = {k: [] for k in requests}
+        for k, ids in requests.items():            # the first five tokens as a portion, beside nothing
+            assert runner.begin_request(k) and cache.manager.reserve(k, 5).ok
+            rows[k].append(runner.step([StepEntry(k, ids[:5], tuple(range(5)))]).logits.float().cpu().clone())
+        for i in range(5, 27):                      # then single tokens of whoever has some left: 3, 2 and 1 requests a step
+            entries = []
+            for k, ids in requests.items():
+                if i < len(ids):
+                    assert cache.manager.reserve(k, 1).ok
+                    entries.append(StepEntry(k, (ids[i],), (0,)))
+            out = runner.step(entries).logits.float().cpu().clone()
+            for j, e in enumerate(entries):
+                rows[e.key].append(out[j : j + 1])
+        for k in requests:
+            runner.end_request(k)
+        assert cache.manager.slots.num_free == 4
+        return {k: torch.cat(v) for k, v in rows.items()}, runner.graph_replays
+
+    recorded, replays = run(True)
+    eager, none = run(False)
+    assert replays >= 15 and none == 0
+    for k, ids in requests.items():
+        assert torch.equal(recorded[k], eager[k]), k
+        x = raw["emb.weight"][torch.tensor(ids)]
+        for p in ("l0.", "l1."):
+            y = plain.rms_norm(x, raw[p + "n1.weight"], 1e-5)
+            state, mixed = torch.zeros(hidden), []
+            for row in y:
+                state = state * decay + row
+                mixed.append(state)
+            x = x + torch.stack(mixed)
+            y = plain.rms_norm(x, raw[p + "n2.weight"], 1e-5)
+            x = x + plain.swiglu(y, raw[p + "ff.gate_proj.weight"], raw[p + "ff.up_proj.weight"], raw[p + "ff.down_proj.weight"])
+        want = plain.linear(plain.rms_norm(x, raw["final.weight"], 1e-5), raw["emb.weight"])
+        gap = (recorded[k] - want).abs().max().item()
+        assert gap <= helpers.tolerance(torch.float32, want), f"{k}: {gap}"
