@@ -36,6 +36,7 @@ FAMILIES: dict[str, list[str]] = {
     "attention_simt": ["attention_simt.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "gemm_tcgen05": ["gemm_tcgen05.cu", "tcgen05.cuh", "common.cuh"],
+    "gemv_mma": ["gemv_mma.cu", "tcgen05.cuh", "common.cuh"],
     "attention_mma": ["attention_mma.cu", "attention_mma.cuh", "common.cuh"],
     "fused_decode": ["fused_decode.cu", "common.cuh"],
     "attention_tcgen05": ["attention_tcgen05.cu", "common.cuh"],

@@ -180,8 +180,37 @@ class PendingSum:
         return self.partial.device
 
 
+class PendingNorm:
+    """RMSNorm(x) * weight of a step of few tokens that has not been computed: `rms_norm` returns
+    one, and the products that can (`qkv_projection`, `linear_swiglu`, `linear` without bias) apply
+    the norm while they stage their operand, which saves the norm's own launch; anything else
+    calls `materialized`, which runs the norm's kernel once and keeps its result in `value`."""
+
+    def __init__(self, x: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+        self.x = x
+        self.weight = weight
+        self.eps = eps
+        self.value = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    @property
+    def dtype(self):
+        return self.x.dtype
+
+    @property
+    def device(self):
+        return self.x.device
+
+
 def materialized(x):
-    """The tensor that `x` stands for (x itself unless it is a PendingSum)."""
+    """The tensor that `x` stands for (x itself unless it is a PendingSum or a PendingNorm)."""
+    if isinstance(x, PendingNorm):
+        if x.value is None:
+            x.value = _rms_norm_now(x.x, x.weight, x.eps)
+        return x.value
     if not isinstance(x, PendingSum):
         return x
     if x.value is None:
@@ -250,12 +279,47 @@ def rms_norm(x, weight: torch.Tensor, eps: float) -> torch.Tensor:
         return normed
     x = materialized(x)
     _need(x, "rms_norm: x")
+    if x.dim() == 2 and _few_tokens(x, x.shape[-1], normed=True):
+        return PendingNorm(x, weight, eps)       # the product that follows applies it
+    return _rms_norm_now(x, weight, eps)
+
+
+def _rms_norm_now(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     out = torch.empty_like(x)
     lib = _lib("elementwise")
     rows = x.numel() // x.shape[-1] if x.numel() else 0
     _check(lib, lib.pae_rms_norm(_ptr(out), _ptr(x), _ptr(weight), rows, (x.shape[-1]), eps,
                                  (_code(x)), _stream()))
     return out
+
+
+# A step of few tokens (decoding) runs a product as one kernel that leaves finished output
+# (csrc/gemv_mma.cu: a warp owns 16 weight rows and the whole K, so no partial sums are left for a
+# kernel of their own, and the norm before and the rotation, SiLU x up or residual after run
+# inside the product) where that is the faster way: where all blocks of that kernel run at once.
+# False sends every product to the tcgen05 kernels and their summing kernels (tests compare the
+# two); `few_token_products_everywhere` sends every product that the kernels can take at all.
+use_few_token_products = True
+few_token_products_everywhere = False
+FEW_TOKENS_MAX = 16
+QKV_KIND, RESIDUAL_KIND, GATE_UP_KIND = 0, 1, 2
+
+
+def _few_tokens(x: torch.Tensor, k: int, normed: bool = False, kind: int = GATE_UP_KIND, n: int = 16) -> bool:
+    """Whether a product of `kind` over x [tokens, K] with `n` weight rows runs as a few-token
+    kernel; `normed`: with the RMSNorm of x folded in (the normed operand has to fit shared memory)."""
+    if not (use_few_token_products and use_tensor_cores and x.dtype == torch.bfloat16 and x.dim() == 2
+            and 0 < x.shape[0] <= FEW_TOKENS_MAX and x.data_ptr() % 16 == 0):
+        return False
+    verdict = _lib("gemv_mma").pae_linear_few_tokens_supports(kind, x.shape[0], n, k, 1 if normed else 0)
+    return verdict == 2 or (verdict == 1 and few_token_products_everywhere)
+
+
+def _norm_of(x):
+    """(input tensor, norm weight or None, eps) of an operand that may be a PendingNorm."""
+    if isinstance(x, PendingNorm) and x.value is None:
+        return x.x, x.weight, x.eps
+    return materialized(x), None, 0.0
 
 
 # The bfloat16 products run on the tcgen05 kernels when the shape allows; set to False to
@@ -295,7 +359,8 @@ def raise_for_error_word(code: int, device) -> None:
                     103: "a page id that is negative or beyond the pool"}.get(int(code), "an index out of range")
             raise KernelError(f"a kernel on device {index} met {what} (bounds code {int(code)}); the access was skipped")
         raise KernelError(
-            f"a tcgen05 kernel on device {index} gave up waiting on an mbarrier (role code {int(code)}); "
+            f"a tensor-core kernel on device {index} gave up waiting on an mbarrier (role code {int(code)}; 8: a warp of a "
+            "few-token product, others: the roles of a tcgen05 kernel); "
             "its output is not valid"
         )
 
@@ -319,6 +384,22 @@ def _tensor_core_shape(x, weight, residual, out_dtype) -> bool:
 
 def linear(x, weight, bias=None, residual=None, out_dtype=None) -> torch.Tensor:
     """x [M, K] . weight [N, K]^T (+ bias [N], float32) (+ residual [M, N]) -> [M, N]."""
+    if (bias is None and out_dtype in (None, torch.bfloat16) and weight.dtype == torch.bfloat16 and weight.dim() == 2
+            and weight.data_ptr() % 16 == 0 and weight.shape[0] <= 65536):
+        source, norm_weight, eps = _norm_of(x)
+        if (_few_tokens(source, weight.shape[1], norm_weight is not None, RESIDUAL_KIND, weight.shape[0]) and source.dim() == 2 and source.shape[1] == weight.shape[1]
+                and source.is_contiguous() and weight.is_contiguous()):
+            residual_now = materialized(residual)
+            m, n = source.shape[0], weight.shape[0]
+            if residual_now is not None:
+                _need(residual_now, "linear: residual", torch.bfloat16)
+                if tuple(residual_now.shape) != (m, n):
+                    raise KernelError(f"linear: residual is {tuple(residual_now.shape)}, the product is [{m}, {n}]")
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=source.device)
+            lib = _lib("gemv_mma")
+            _check(lib, lib.pae_linear_few_tokens(_ptr(out), _ptr(source), _ptr(weight), _ptr(residual_now), _ptr(norm_weight),
+                                                  eps, m, n, weight.shape[1], _ptr(_error_flag(source.device)), _stream()))
+            return out
     x = materialized(x)
     residual = materialized(residual)
     _need(x, "linear: x")
@@ -436,6 +517,30 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
     for few tokens fuse the other way round (the split sum runs inside the rotation kernel)."""
     m, k = x.shape
     n = weight.shape[0]
+    source, norm_weight, eps = _norm_of(x)
+    if (_few_tokens(source, k, norm_weight is not None, QKV_KIND, n) and weight.dtype == torch.bfloat16 and weight.is_contiguous() and weight.data_ptr() % 16 == 0
+            and n == (num_heads + 2 * num_kv_heads) * head_dim and weight.shape[1] == k and head_dim % 16 == 0
+            and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
+        _need(source, "qkv_projection: x")
+        if bias is not None:
+            _need(bias, "qkv_projection: bias", torch.float32)
+        if table is not None:
+            _need(table, "qkv_projection: table", torch.float32)
+            if tuple(table.shape) != (m, head_dim):
+                raise KernelError(f"qkv_projection: table is {tuple(table.shape)}, [{m}, {head_dim}] is needed")
+        if slots is not None:
+            _need(slots, "qkv_projection: slots", torch.int32)
+            _need(keys, "qkv_projection: keys", torch.bfloat16)
+            _need(values, "qkv_projection: values", torch.bfloat16)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=source.device)
+        lib = _lib("gemv_mma")
+        _set_bounds("gemv_mma", keys if slots is not None else None)
+        _check(lib, lib.pae_qkv_few_tokens(
+            _ptr(out), _ptr(source), _ptr(weight), _ptr(bias), _ptr(norm_weight), eps, _ptr(table), _ptr(slots),
+            _ptr(keys if slots is not None else None), _ptr(values if slots is not None else None), m, num_heads,
+            num_kv_heads, head_dim, page_size, k, _ptr(_error_flag(source.device)), _stream()))
+        return out
+    x = materialized(x)
     if (fuse_qkv_epilogue and m > SWAPPED_MAX_TOKENS and n >= 256 and n == (num_heads + 2 * num_kv_heads) * head_dim
             and weight.shape[1] == k and not isinstance(x, PendingSum) and _tensor_core_shape(x, weight, None, x.dtype)
             and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
@@ -613,6 +718,16 @@ def linear_swiglu(x, weight) -> torch.Tensor:
     tokens the activation runs in the product's epilogue; with few, in the kernel that sums the
     splits; otherwise as a kernel of its own. Gate and up are rounded to the engine dtype first in
     every one of them, so all give the same bits."""
+    source, norm_weight, eps = _norm_of(x)
+    if (_few_tokens(source, weight.shape[1], norm_weight is not None, GATE_UP_KIND, weight.shape[0]) and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+            and weight.data_ptr() % 16 == 0 and weight.shape[0] % 32 == 0 and source.shape[1] == weight.shape[1]):
+        _need(source, "linear_swiglu: x")
+        out = torch.empty((source.shape[0], weight.shape[0] // 2), dtype=torch.bfloat16, device=source.device)
+        lib = _lib("gemv_mma")
+        _check(lib, lib.pae_linear_swiglu_few_tokens(_ptr(out), _ptr(source), _ptr(weight), _ptr(norm_weight), eps,
+                                                     source.shape[0], weight.shape[0], weight.shape[1],
+                                                     _ptr(_error_flag(source.device)), _stream()))
+        return out
     x = materialized(x)
     m, k = x.shape
     n = weight.shape[0]

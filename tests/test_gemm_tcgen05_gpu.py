@@ -1,5 +1,7 @@
 """The tcgen05 products against the plain reference: the many-token form and the few-token
-(swapped, split-K) form, at sizes with ragged edges in every dimension."""
+(swapped, split-K) form, at sizes with ragged edges in every dimension. The mma.sync kernels
+that take products of up to 16 tokens where they are faster are switched off in this module
+(tests/test_gemv_mma_gpu.py is theirs)."""
 
 import pytest
 import torch
@@ -14,7 +16,10 @@ def ops():
     from paged_attention_engine_b200.kernels import ops as kernel_ops
 
     kernel_ops.use_tensor_cores = True
-    return kernel_ops
+    before = kernel_ops.use_few_token_products
+    kernel_ops.use_few_token_products = False
+    yield kernel_ops
+    kernel_ops.use_few_token_products = before
 
 
 def _rand(shape, seed, std=1.0):
