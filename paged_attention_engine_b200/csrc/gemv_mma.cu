@@ -47,8 +47,8 @@ namespace {
 using pae_tcgen05::mbar_expect_tx;
 using pae_tcgen05::mbar_init;
 using pae_tcgen05::mbar_try_wait;
-using pae_tcgen05::tensor_map;
-using pae_tcgen05::tma_load_2d;
+using pae_tcgen05::encode_tiled;
+using pae_tcgen05::EncodeTiled;
 
 constexpr int ROWS = 16;            // weight rows per warp (the MMA's M)
 constexpr int CHUNK = 64;           // of K per stage
@@ -68,6 +68,18 @@ __device__ __forceinline__ void mma_16816(float* d, const uint32_t* a, uint32_t 
   asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One copy of `box_rows` rows x BOXES neighbouring chunks of 64 of K: the matrix is described to
+// the TMA unit as [K / 64][rows][64], so that a box of (64, box_rows, BOXES) lands as BOXES tiles
+// of box_rows x 128 bytes, each swizzled by itself. One instruction per stage and operand
+// instead of one per chunk: at a kilobyte an instruction the TMA unit's instruction rate, not
+// memory, set the pace of an SM.
+__device__ __forceinline__ void tma_load_chunks(uint32_t dst, const CUtensorMap* map, uint32_t bar, int row, int chunk) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(row), "r"(chunk)
+      : "memory");
 }
 
 enum Kind : int { QKV = 0, RESIDUAL = 1, GATE_UP = 2 };
@@ -161,27 +173,23 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
   }
   __syncwarp();
 
-  // A stage holds up to BOXES neighbouring chunks, asked for together (a row's bytes of one stage
-  // are neighbours in memory). Weights: rows row_lo.. and row_hi.., 8 each (rows beyond the matrix read as zero).
+  // A stage holds BOXES neighbouring chunks, asked for together (a row's bytes of one stage are
+  // neighbours in memory): BOXES tiles of rows row_lo.., BOXES tiles of rows row_hi.., 8 rows
+  // each, then BOXES tiles of the activations. Rows beyond the matrix and chunks beyond K read as zero.
   const int groups = (count + BOXES - 1) / BOXES;
   auto fetch_weights = [&](int group) {
-    const int stage = group % STAGES, boxes = min(BOXES, count - group * BOXES);
-    const uint32_t bar = bar0 + stage * 8;
-    mbar_expect_tx(bar, boxes * BOX_BYTES);
+    const int stage = group % STAGES;
+    const uint32_t bar = bar0 + stage * 8, dst = mine_u32 + stage * STAGE_BYTES;
+    mbar_expect_tx(bar, STAGE_BYTES);
     if (SELFTEST && warp == p.skip_warp && group == p.skip_group) return;
-    for (int b = 0; b < boxes; ++b) {
-      const uint32_t dst = mine_u32 + stage * STAGE_BYTES + b * BOX_BYTES;
-      const int x = (first + group * BOXES + b) * CHUNK;
-      tma_load_2d(dst, &map_w, bar, x, row_lo);
-      tma_load_2d(dst + A_BYTES / 2, &map_w, bar, x, row_hi);
-    }
+    tma_load_chunks(dst, &map_w, bar, row_lo, first + group * BOXES);
+    tma_load_chunks(dst + BOXES * (A_BYTES / 2), &map_w, bar, row_hi, first + group * BOXES);
   };
   auto fetch_activations = [&](int group) {
     if (NORMED) return;
-    const int stage = group % STAGES, boxes = min(BOXES, count - group * BOXES);
+    const int stage = group % STAGES;
     if (SELFTEST && warp == p.skip_warp && group == p.skip_group) return;
-    for (int b = 0; b < boxes; ++b)
-      tma_load_2d(mine_u32 + stage * STAGE_BYTES + b * BOX_BYTES + A_BYTES, &map_x, bar0 + stage * 8, (first + group * BOXES + b) * CHUNK, 0);
+    tma_load_chunks(mine_u32 + stage * STAGE_BYTES + BOXES * A_BYTES, &map_x, bar0 + stage * 8, 0, first + group * BOXES);
   };
 
   // The first stages' weights before the wait for the kernel before; their activations after it.
@@ -201,12 +209,28 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
       bias_hi = p.bias[qkv_head * p.d + half + qkv_f];
     }
   }
+  // ... and so does the first pass of the norm's weight (NORMED).
+  constexpr int PASS = 8;              // 16-byte units of a token's x per lane and pass
+  const int units = p.k >> 3;
+  float4 gamma0[PASS][2];
+  if (NORMED) {
+#pragma unroll
+    for (int j = 0; j < PASS; ++j) {
+      const int u = 32 * j + lane;
+      gamma0[j][0] = gamma0[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (u < units) {
+        gamma0[j][0] = *(const float4*)(p.norm_weight + u * 8);
+        gamma0[j][1] = *(const float4*)(p.norm_weight + u * 8 + 4);
+      }
+    }
+  }
   dependent_launch_wait();
   if (lane == 0)
     for (int i = 0; i < early; ++i) fetch_activations(i);
   // ... or from the step (angles and slots, the residual) and is asked for here, a trip to the
   // L2 that the main loop hides: for tokens 8 n + 2 t4 + e.
-  float side_lo[NT8][2], side_hi[NT8][2];        // QKV: cosine and sine; RESIDUAL: the residual of rows g and g + 8
+  float side_lo[NT8][2], side_hi[NT8][2];        // QKV: cosine and sine
+  __nv_bfloat16 rest_lo[NT8][2], rest_hi[NT8][2];   // RESIDUAL: the residual of rows g and g + 8, converted where it is added
   int side_slot[NT8][2];
 #pragma unroll
   for (int n = 0; n < NT8; ++n) {
@@ -216,6 +240,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
       side_lo[n][e] = KIND == QKV ? 1.f : 0.f;
       side_hi[n][e] = 0.f;
       side_slot[n][e] = -1;
+      rest_lo[n][e] = rest_hi[n][e] = __float2bfloat16_rn(0.f);
       if (!finishes || token >= p.tokens) continue;
       if (KIND == QKV) {
         if (qkv_head < p.heads + p.kv_heads && p.rotary != nullptr) {
@@ -225,51 +250,64 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
         if (qkv_head >= p.heads && p.slots != nullptr) side_slot[n][e] = p.slots[token];
       } else if (KIND == RESIDUAL && p.residual != nullptr) {
         const int r0 = tile * ROWS + g;
-        if (r0 < p.n) side_lo[n][e] = __bfloat162float(p.residual[(size_t)token * p.n + r0]);
-        if (r0 + 8 < p.n) side_hi[n][e] = __bfloat162float(p.residual[(size_t)token * p.n + r0 + 8]);
+        if (r0 < p.n) rest_lo[n][e] = p.residual[(size_t)token * p.n + r0];
+        if (r0 + 8 < p.n) rest_hi[n][e] = p.residual[(size_t)token * p.n + r0 + 8];
       }
     }
   }
 
   if (NORMED) {
-    // The block's operand: a warp takes tokens warp, warp + WARPS, ...; a lane 16 bytes of x at a time.
-    const int units = p.k >> 3;
-    for (int r = warp; r < TOKENS; r += WARPS) {
-      float sq = 0.f;
-      for (int u0 = 0; u0 < units; u0 += 128) {
-        uint4 v[4];
-        float4 w[4][2];
+    // The block's operand: warp w takes tokens w, w + WARPS, ...; a lane 16 bytes of x at a time,
+    // PASS of them per token asked for together, so that a K of up to 2,048 costs one trip to the L2.
+    float sq[TOKENS / WARPS > 0 ? TOKENS / WARPS : 1] = {};
+    constexpr int MINE = TOKENS / WARPS > 0 ? TOKENS / WARPS : 1;      // tokens per warp
+    for (int u0 = 0; u0 < units; u0 += 32 * PASS) {
+      uint4 v[MINE][PASS];
+      float4 w[PASS][2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + 32 * j + lane;
-          v[j] = make_uint4(0, 0, 0, 0);
-          if (u < units && r < p.tokens) {
-            v[j] = *(const uint4*)(p.x + (size_t)r * p.k + u * 8);
-            w[j][0] = *(const float4*)(p.norm_weight + u * 8);
-            w[j][1] = *(const float4*)(p.norm_weight + u * 8 + 4);
-          } else {
-            w[j][0] = w[j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+      for (int j = 0; j < PASS; ++j) {
+        const int u = u0 + 32 * j + lane;
+#pragma unroll
+        for (int m = 0; m < MINE; ++m) {
+          const int r = warp + m * WARPS;
+          v[m][j] = make_uint4(0, 0, 0, 0);
+          if (u < units && r < p.tokens) v[m][j] = *(const uint4*)(p.x + (size_t)r * p.k + u * 8);
         }
+        if (u0 == 0) {
+          w[j][0] = gamma0[j][0];
+          w[j][1] = gamma0[j][1];
+        } else if (u < units) {
+          w[j][0] = *(const float4*)(p.norm_weight + u * 8);
+          w[j][1] = *(const float4*)(p.norm_weight + u * 8 + 4);
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int u = u0 + 32 * j + lane;
-          if (u >= units) continue;
-          const uint32_t in[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-          const float ws[8] = {w[j][0].x, w[j][0].y, w[j][0].z, w[j][0].w, w[j][1].x, w[j][1].y, w[j][1].z, w[j][1].w};
+      for (int j = 0; j < PASS; ++j) {
+        const int u = u0 + 32 * j + lane;
+        if (u >= units) continue;
+        const float ws[8] = {w[j][0].x, w[j][0].y, w[j][0].z, w[j][0].w, w[j][1].x, w[j][1].y, w[j][1].z, w[j][1].w};
+#pragma unroll
+        for (int m = 0; m < MINE; ++m) {
+          const int r = warp + m * WARPS;
+          if (r >= TOKENS) continue;
+          const uint32_t in[4] = {v[m][j].x, v[m][j].y, v[m][j].z, v[m][j].w};
           // unit u = k 8u..8u+7: half u & 1 (b0 or b1) of step u >> 1; its pair t goes to lane (r & 7) * 4 + t
           uint8_t* to = operand + operand_offset<NT8>(u >> 1, r >> 3, (r & 7) * 4) + (u & 1) * 4;
 #pragma unroll
           for (int t = 0; t < 4; ++t) {
             const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)&in[t]);
-            sq += f.x * f.x + f.y * f.y;
+            sq[m] += f.x * f.x + f.y * f.y;
             const __nv_bfloat162 scaled = __floats2bfloat162_rn(f.x * ws[2 * t], f.y * ws[2 * t + 1]);
             *(uint32_t*)(to + t * 8) = *(const uint32_t*)&scaled;
           }
         }
       }
-      sq = warp_sum(sq);
-      if (lane == 0) token_scale[r] = rsqrtf(sq / (float)p.k + p.eps);
+    }
+#pragma unroll
+    for (int m = 0; m < MINE; ++m) {
+      const int r = warp + m * WARPS;
+      const float total = warp_sum(sq[m]);
+      if (lane == 0 && r < TOKENS) token_scale[r] = rsqrtf(total / (float)p.k + p.eps);
     }
     __syncthreads();
   }
@@ -299,14 +337,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
 #pragma unroll
     for (int b = 0; b < BOXES; ++b) {
       if (b >= boxes) break;
-      const uint32_t a_tile = mine_u32 + stage * STAGE_BYTES + b * BOX_BYTES;
-      const uint8_t* b_tile = mine + stage * STAGE_BYTES + b * BOX_BYTES + A_BYTES;
+      const uint32_t a_tile = mine_u32 + stage * STAGE_BYTES + b * (A_BYTES / 2);
+      const uint8_t* b_tile = mine + stage * STAGE_BYTES + BOXES * A_BYTES + b * B_BYTES;
       const int step0 = (first + i * BOXES + b) * (CHUNK / 16);
 #pragma unroll
       for (int s = 0; s < CHUNK / 16; ++s) {
         uint32_t a[4];
         // matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
-        ldmatrix_x4(a, a_tile + tile_offset((lane & 7) + ((lane >> 3) & 1) * 8, s * 2 + (lane >> 4)));
+        ldmatrix_x4(a, a_tile + ((lane >> 3) & 1) * (BOXES * (A_BYTES / 2)) + tile_offset(lane & 7, s * 2 + (lane >> 4)));
 #pragma unroll
         for (int n = 0; n < NT8; ++n) {
           uint32_t b0, b1;
@@ -405,11 +443,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
       } else {
         const int row_lo = tile * ROWS + g, row_hi = row_lo + 8;
         if (row_lo < p.n) {
-          lo += side_lo[n][e];
+          lo += __bfloat162float(rest_lo[n][e]);
           p.out[(size_t)token * p.n + row_lo] = __float2bfloat16_rn(lo);
         }
         if (row_hi < p.n) {
-          hi += side_hi[n][e];
+          hi += __bfloat162float(rest_hi[n][e]);
           p.out[(size_t)token * p.n + row_hi] = __float2bfloat16_rn(hi);
         }
       }
@@ -417,6 +455,48 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
   }
 }
 
+
+struct ChunkMapKey {
+  const void* ptr;
+  int rows, k, box_rows, boxes;
+  bool operator==(const ChunkMapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows && boxes == o.boxes; }
+};
+struct ChunkMapKeyHash {
+  size_t operator()(const ChunkMapKey& key) const {
+    size_t h = (size_t)key.ptr;
+    h = h * 1000003u ^ (size_t)key.rows;
+    h = h * 1000003u ^ (size_t)key.k;
+    h = h * 1000003u ^ (size_t)key.box_rows;
+    return h * 1000003u ^ (size_t)key.boxes;
+  }
+};
+
+// A [rows, k] bfloat16 row-major matrix as [k / 64][rows][64] (strides 128 bytes, k * 2 bytes,
+// one element), boxes of 64 x box_rows x boxes with 128-byte swizzle, zero fill outside.
+int chunk_map(CUtensorMap* out, const void* ptr, int rows, int k, int box_rows, int boxes) {
+  static std::mutex mutex;
+  static std::unordered_map<ChunkMapKey, CUtensorMap, ChunkMapKeyHash> cache;
+  std::lock_guard<std::mutex> guard(mutex);
+  const ChunkMapKey key{ptr, rows, k, box_rows, boxes};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *out = found->second;
+    return 0;
+  }
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return fail(101, "linear_few_tokens: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[3] = {(cuuint64_t)CHUNK, (cuuint64_t)rows, (cuuint64_t)(k / CHUNK)};
+  const cuuint64_t strides[2] = {(cuuint64_t)k * 2, (cuuint64_t)CHUNK * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)CHUNK, (cuuint32_t)box_rows, (cuuint32_t)boxes};
+  const cuuint32_t element_strides[3] = {1, 1, 1};
+  CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, element_strides,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(102, "linear_few_tokens: cuTensorMapEncodeTiled failed with %d for [%d, %d]", (int)r, rows, k);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
 
 template <int KIND, int NT8, int WARPS, bool SPLIT, int STAGES, int BOXES, bool NORMED>
 constexpr size_t shared_bytes(int k) {
@@ -439,9 +519,9 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
     configured = bytes;
   }
   CUtensorMap map_w, map_x;
-  if (int err = tensor_map(&map_w, w, p.n, p.k, 8)) return err;
+  if (int err = chunk_map(&map_w, w, p.n, p.k, 8, BOXES)) return err;
   if (NORMED) map_x = map_w;       // not read
-  else if (int err = tensor_map(&map_x, p.x, p.tokens, p.k, 8 * NT8)) return err;
+  else if (int err = chunk_map(&map_x, p.x, p.tokens, p.k, 8 * NT8, BOXES)) return err;
   const int blocks = SPLIT ? tiles : (tiles + WARPS - 1) / WARPS;
   launch_kernel(kernel, dim3(blocks), dim3(WARPS * 32), bytes, stream, map_w, map_x, p);
   return check_launch("linear_few_tokens");
@@ -449,15 +529,18 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
 
 // What decides the shape of a launch: warps per block, stages per warp's ring and chunks per
 // stage. What counts is how many neighbouring bytes of a weight row are asked for at once (a
-// stage of 4 chunks: 512) and how much is on the way per SM (warps x stages x chunks x 2 KB);
-// measured at 8 tokens, q|k|v, o, gate|up and down of a 1536-wide model in a row, 28 times
-// over: 25.8 us with 2 stages of 4 chunks, 27.1 us with 4 of 2, 30.9 us with 2 of 2, 33.1 us with
-// 8 of 1, 50.2 us with 4 of 1. The first of these that fits shared memory is taken, unless
-// `pae_linear_few_tokens_configure` has named one for the kind.
+// stage of 4 chunks: 512), how much is on the way per SM (warps x stages x chunks x 2 KB) and how
+// much of a warp's share of K the ring holds when the wait for the kernel before ends: what it
+// does not hold costs further trips to memory one after the other. Measured at 8 tokens (q|k|v, o,
+// gate|up and down of a 1536-wide model in a row, 28 times over, one copy per stage and operand):
+// 23.4 us with 3 stages of 3 chunks, 24.0 us with 2 of 4, 24.4 us with 4 of 2, 27.0 us with 2 of 2;
+// with one copy per chunk 25.8 us (2 of 4), 33.1 us (8 of 1), 50.2 us (4 of 1). The first in the
+// order of preference whose blocks all run at once is taken (gate|up alone is fastest with 3 stages
+// of 4), unless `pae_linear_few_tokens_configure` has named one for the kind.
 struct Shape {
   int warps, stages, boxes;
 };
-constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 4, 2}, {8, 2, 2}};
+constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 4, 2}, {8, 2, 2}, {8, 3, 3}, {8, 3, 4}};
 constexpr int NUM_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
 int g_forced[3] = {-1, -1, -1};        // index into SHAPES, or -1
 
@@ -466,7 +549,9 @@ size_t shape_bytes(int index, int k) {
   switch (index) {
     case 0: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 4, NORMED>(k);
     case 1: return shared_bytes<KIND, NT8, 8, SPLIT, 4, 2, NORMED>(k);
-    default: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(k);
+    case 2: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(k);
+    case 3: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(k);
+    default: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(k);
   }
 }
 
@@ -493,7 +578,10 @@ template <int KIND, int NT8, bool SPLIT, bool NORMED>
 int pick_shape(int k, long blocks, bool* at_once = nullptr) {
   if (at_once != nullptr) *at_once = false;
   int fits = -1;
-  for (int i = 0; i < NUM_SHAPES; ++i) {
+  // indices into SHAPES in the order of preference
+  static constexpr int NORMED_ORDER[NUM_SHAPES] = {4, 0, 3, 1, 2}, PLAIN_ORDER[NUM_SHAPES] = {3, 0, 1, 2, 4};
+  for (int at = 0; at < NUM_SHAPES; ++at) {
+    const int i = NORMED ? NORMED_ORDER[at] : PLAIN_ORDER[at];
     if (g_forced[KIND] >= 0 && i != g_forced[KIND]) continue;
     const size_t bytes = shape_bytes<KIND, NT8, SPLIT, NORMED>(i, k);
     if (bytes > (size_t)SMEM_LIMIT) continue;
@@ -512,6 +600,8 @@ int launch_shape(const Params& p, const void* w, int tiles, cudaStream_t stream)
     case 0: return launch_one<KIND, NT8, 8, SPLIT, 2, 4, NORMED>(p, w, tiles, stream);
     case 1: return launch_one<KIND, NT8, 8, SPLIT, 4, 2, NORMED>(p, w, tiles, stream);
     case 2: return launch_one<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(p, w, tiles, stream);
+    case 3: return launch_one<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(p, w, tiles, stream);
+    case 4: return launch_one<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(p, w, tiles, stream);
   }
   return fail(2, "linear_few_tokens: %d tokens x K = %d do not fit shared memory", p.tokens, p.k);
 }
@@ -663,8 +753,8 @@ PAE_EXPORT int pae_linear_few_tokens_selftest_giveup(void* out, const void* x, c
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
   if (err != cudaSuccess) return fail(100, "linear_few_tokens_selftest_giveup: %s", cudaGetErrorString(err));
   CUtensorMap map_w, map_x;
-  if (int e = tensor_map(&map_w, w, n, k, 8)) return e;
-  if (int e = tensor_map(&map_x, x, tokens, k, 8)) return e;
+  if (int e = chunk_map(&map_w, w, n, k, 8, 2)) return e;
+  if (int e = chunk_map(&map_x, x, tokens, k, 8, 2)) return e;
   launch_kernel(kernel, dim3((n + ROWS - 1) / ROWS), dim3(256), bytes, (cudaStream_t)stream, map_w, map_x, p);
   return check_launch("linear_few_tokens_selftest_giveup");
 }

@@ -13,7 +13,7 @@ import torch_ops as ref
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(8, 2, 4), (8, 4, 2), (8, 2, 2)]
+SHAPES = [(8, 2, 4), (8, 4, 2), (8, 2, 2), (8, 3, 3), (8, 3, 4)]
 QKV, RESIDUAL, GATE_UP = 0, 1, 2
 
 
@@ -185,14 +185,14 @@ def test_every_built_shape_gives_the_same_bits(ops, tokens):
             for product, seen in zip(products, results):
                 try:
                     seen.append(product())
-                except ops.KernelError as refused:      # 16 tokens' activations beside the weights in the widest rings
-                    assert "shared memory" in str(refused) and tokens > 8
+                except ops.KernelError as refused:      # activations beside the weights in the widest rings
+                    assert "shared memory" in str(refused) and (tokens > 8 or (stages, boxes) == (3, 4))
     finally:
         for kind in range(3):
             assert lib.pae_linear_few_tokens_configure(kind, 0, 0, 0) == 0
     ops.check_device_errors()
     for product, seen in zip(products, results):
-        assert len(seen) == 3 or (tokens > 8 and len(seen) >= 1)
+        assert len(seen) >= 4 or (tokens > 8 and len(seen) >= 1)
         seen.append(product())                         # the library's own choice
         for other in seen[1:]:
             assert torch.equal(seen[0], other)
