@@ -76,6 +76,10 @@ class ModelRunner:
         # The token last sampled for the request in each state slot; a step's token id of -1
         # reads it, so a sampled token can feed the next step without a trip to the host.
         self.last_token = torch.zeros(self.manager.slots.num_slots + 1, dtype=torch.int32, device=self.runtime.device)
+        # The device's error word exists before any step is recorded: made inside a recording, its
+        # zero-fill would be part of the graph and clear the word at every replay.
+        if self.runtime.device.type == "cuda" and hasattr(self.runtime.ops, "error_flag"):
+            self.runtime.ops.error_flag(self.runtime.device)
 
     def begin_request(self, key: Hashable) -> bool:
         """Registers a request (state slot, empty block tables); False when no slot is free."""
