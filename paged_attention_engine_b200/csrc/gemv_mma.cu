@@ -512,11 +512,14 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
   const size_t bytes = shared_bytes<KIND, NT8, WARPS, SPLIT, STAGES, BOXES, NORMED>(p.k);
   if (bytes > (size_t)SMEM_LIMIT) return fail(2, "linear_few_tokens: %d tokens x K = %d need %zu bytes of shared memory", p.tokens, p.k, bytes);
   auto kernel = gemv_kernel<KIND, NT8, WARPS, SPLIT, STAGES, BOXES, NORMED>;
-  static size_t configured = 0;
-  if (bytes > configured) {
+  // The attribute belongs to the kernel as loaded on one device.
+  static size_t configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return fail(100, "linear_few_tokens: no current device");
+  if (bytes > configured[device]) {
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (err != cudaSuccess) return fail(100, "linear_few_tokens: %s", cudaGetErrorString(err));
-    configured = bytes;
+    configured[device] = bytes;
   }
   CUtensorMap map_w, map_x;
   if (int err = chunk_map(&map_w, w, p.n, p.k, 8, BOXES)) return err;
@@ -627,7 +630,7 @@ int check_common(const char* what, const void* w, const void* x, const void* nor
 }  // namespace
 
 template <int KIND, bool SPLIT>
-int verdict(int tokens, long blocks, int k, int normed) {
+int answer(int tokens, long blocks, int k, int normed) {
   bool at_once = false;
   int shape;
   if (tokens <= 8) shape = normed ? pick_shape<KIND, 1, SPLIT, true>(k, blocks, &at_once) : pick_shape<KIND, 1, SPLIT, false>(k, blocks, &at_once);
@@ -642,9 +645,9 @@ int verdict(int tokens, long blocks, int k, int normed) {
 PAE_EXPORT int pae_linear_few_tokens_supports(int kind, int tokens, int n, int k, int normed) {
   if (tokens < 1 || tokens > MAX_TOKENS || k < CHUNK || k % CHUNK || n < 1) return 0;
   const long tiles = (n + ROWS - 1) / ROWS;
-  if (kind == QKV) return verdict<QKV, true>(tokens, tiles, k, normed);
-  if (kind == RESIDUAL) return verdict<RESIDUAL, true>(tokens, tiles, k, normed);
-  if (kind == GATE_UP) return verdict<GATE_UP, false>(tokens, (tiles + 7) / 8, k, normed);
+  if (kind == QKV) return answer<QKV, true>(tokens, tiles, k, normed);
+  if (kind == RESIDUAL) return answer<RESIDUAL, true>(tokens, tiles, k, normed);
+  if (kind == GATE_UP) return answer<GATE_UP, false>(tokens, (tiles + 7) / 8, k, normed);
   return 0;
 }
 

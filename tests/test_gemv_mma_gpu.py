@@ -239,7 +239,7 @@ def test_what_is_refused(ops):
 
 
 def test_where_the_kernels_layer_sends_a_product(ops):
-    """To these kernels where all blocks of the launch run at once (verdict 2): the four products of
+    """To these kernels where all blocks of the launch run at once (the library answers 2): the four products of
     the 1536-wide model do, q|k|v and gate|up of the 3584-wide one do not and stay with tcgen05."""
     lib = ops._lib("gemv_mma")
     sms = ops._lib("gemm_tcgen05").pae_sm_count()
