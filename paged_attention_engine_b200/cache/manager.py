@@ -132,7 +132,7 @@ class StateSlotPool:
 
     def release(self, key: Hashable) -> int:
         slot = self._owner.pop(key)
-        self._free.append(slot)
+        self._free.appendleft(slot)      # the next request takes it: steps of the same shape then meet the same slots again
         return slot
 
     def slot_of(self, key: Hashable) -> int:

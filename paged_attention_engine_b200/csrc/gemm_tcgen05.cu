@@ -701,13 +701,21 @@ int launch_persistent_with(const Params& p, const void* a, const void* b, int k,
 }
 
 // The tile width whose walk over the output costs least: rounds of tiles over the SMs
-// times (width + a fixed share for a tile's first loads and its epilogue).
+// times (width + a fixed share for a tile's first loads and its epilogue). The narrow widths
+// serve a portion of a few hundred tokens, whose few wide tiles would leave most SMs idle
+// (q|k|v of 128 tokens: 8 tiles of 256 columns, 18.1 us with 16 of 128 against 23.7); they are
+// left out where a long K is shared out over blocks instead (a plain product with 32 k-blocks
+// and more: `pae_linear_tcgen05_plane_count`), because a narrow tile reads the tokens' operand
+// from L2 once more per 64 columns (down of 512 tokens: 42 us with 96 tiles of 64 columns and
+// the whole K each, 21.5 us with 36 tiles of 176 in four planes).
 int persistent_width(const Params& p) {
-  const int widths[3] = {256, 192, 176};
+  const int widths[5] = {256, 192, 176, 128, 64};
   const int tiles_a = (p.rows_a + BM - 1) / BM;
+  const bool narrow = p.swiglu || p.rotary || p.k_blocks < 32;
   int best = 256;
   long best_cost = -1;
   for (int w : widths) {
+    if (w < 176 && !narrow) continue;
     if (p.swiglu && w % 32) continue;         // a tile must not cut a gate block from its up block
     if (p.rotary && w % p.head_dim) continue; // nor a head
     const int tiles = tiles_a * ((p.rows_b + w - 1) / w);
@@ -724,6 +732,8 @@ int launch_persistent(const Params& p, const void* a, const void* b, int k, cuda
   const int best = persistent_width(p);
   if (best == 192) return launch_persistent_with<192>(p, a, b, k, stream);
   if (best == 176) return launch_persistent_with<176>(p, a, b, k, stream);
+  if (best == 128) return launch_persistent_with<128>(p, a, b, k, stream);
+  if (best == 64) return launch_persistent_with<64>(p, a, b, k, stream);
   return launch_persistent_with<256>(p, a, b, k, stream);
 }
 
@@ -821,19 +831,24 @@ PAE_EXPORT int pae_linear_tcgen05(void* out, const void* x, const void* w, const
 
 // How many float32 planes `pae_linear_tcgen05_planes` writes for this shape: 1 (call
 // `pae_linear_tcgen05` instead) unless the output has so few tiles that they leave more than
-// half of the SMs idle while K is long (a down projection for a few hundred tokens): then
-// each tile's K is shared out over as many blocks as fill the SMs, 8 k-blocks each at least.
+// half of the SMs idle (a projection for one or two hundred tokens; a down projection for a few
+// hundred): then each tile's K is shared out over as many blocks as fill the SMs, 8 k-blocks
+// each at least where K is long (32 k-blocks and more), 4 where it is short. What a block can
+// draw from memory is a fraction of what the GPU can, so a product of few tiles runs at the
+// speed of few SMs whatever its size (q|k|v of 128 tokens on 16 tiles: 18 us for 6 MB of weights).
 PAE_EXPORT int pae_linear_tcgen05_plane_count(int tokens, int n, int k) {
   const int k_blocks = (k + BK - 1) / BK;
-  if (tokens <= 64 || n < 256 || k_blocks < 32) return 1;
+  if (tokens <= 64 || n < 256 || k_blocks < 8) return 1;
+  const int least = k_blocks >= 32 ? 8 : 4;
   Params p{};
   p.rows_a = tokens;
   p.rows_b = n;
+  p.k_blocks = k_blocks;
   const int width = persistent_width(p);
   const int tiles = ((tokens + BM - 1) / BM) * ((n + width - 1) / width);
   if (tiles * 2 > sm_count()) return 1;
   int planes = sm_count() / tiles;
-  planes = planes > k_blocks / 8 ? k_blocks / 8 : planes;
+  planes = planes > k_blocks / least ? k_blocks / least : planes;
   if (planes < 2) return 1;
   const int per = (k_blocks + planes - 1) / planes;
   return (k_blocks + per - 1) / per;
@@ -879,7 +894,7 @@ PAE_EXPORT int pae_linear_swapped_splits(int n, int k) {
 PAE_EXPORT int pae_linear_tcgen05_swapped(float* partial, const void* x, const void* w, int tokens, int n, int k,
                                           int* error, void* stream) {
   if (tokens == 0 || n == 0) return 0;
-  if (tokens > 64) return fail(2, "linear_tcgen05_swapped: %d tokens are more than the 64 it takes", tokens);
+  if (tokens > 128) return fail(2, "linear_tcgen05_swapped: %d tokens are more than the 128 it takes", tokens);
   if (int err = check_operands(x, w, k)) return err;
   const int splits = pae_linear_swapped_splits(n, k);
   Params p{};
@@ -894,7 +909,8 @@ PAE_EXPORT int pae_linear_tcgen05_swapped(float* partial, const void* x, const v
   cudaStream_t s = (cudaStream_t)stream;
   if (tokens <= 16) return launch<16, SWAPPED>(p, w, x, k, splits, s);
   if (tokens <= 32) return launch<32, SWAPPED>(p, w, x, k, splits, s);
-  return launch<64, SWAPPED>(p, w, x, k, splits, s);
+  if (tokens <= 64) return launch<64, SWAPPED>(p, w, x, k, splits, s);
+  return launch<128, SWAPPED>(p, w, x, k, splits, s);
 }
 
 // The self-test of the give-up path: `pae_linear_tcgen05_swapped` for at most 16 tokens, except

@@ -12,10 +12,21 @@ launch-bound: some hundreds of small kernels. Such a step is captured once per (
 size, block-table width) into a CUDA graph whose kernels read the step's integers from a
 fixed device buffer, and replayed afterwards. The graph holds the same kernels as the
 eager step; what it computes does not differ.
+
+Any other step costs its launches' host time (some 200 launches of 14 microseconds), which is
+more than the GPU needs for a portion of a few hundred tokens. A step whose SHAPE comes again
+(the same number of tokens, start, wanted places and state slot for every entry, in order: the
+first portion of a long prompt under a token budget, a prompt length that repeats) is recorded
+at its second appearance and replayed from then on; a few such recordings are kept, the least
+recently used one goes first. Everything that the host knows of such a step (`host_q_lens`,
+`host_q_pos0`, `host_state_slots`, what the kernels' wrappers plan from them) follows from its
+shape, so the recording holds exactly the eager step's launches; token ids, pages and slots in
+the pages are read from the step's device buffer, which every replay refills.
 """
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Any, Hashable, Sequence
 
@@ -45,6 +56,7 @@ class _DecodeGraph:
         self.logits: torch.Tensor | None = None
         self.tokens: torch.Tensor | None = None
         self.launches = 0
+        self.num_tokens = 0
 
 
 class ModelRunner:
@@ -56,6 +68,12 @@ class ModelRunner:
     # keys, not to the block table's width, which is a power of two (at context 4,097 the table
     # is 8,192 keys wide, and slices planned for 8,192 keys would be twice as long as needed).
     KV_BUCKET = 512
+    # Recordings of steps that are not decode-only, by exact shape: how many are kept, how many
+    # shapes are remembered as seen once, and the largest step (tokens, entries) that is recorded.
+    SHAPE_GRAPHS = 8
+    SHAPES_REMEMBERED = 256
+    SHAPE_GRAPH_MAX_TOKENS = 8192
+    SHAPE_GRAPH_MAX_ENTRIES = 16
 
     def __init__(self, model: DecoderModel, cache: PagedKVCache, use_graphs: bool = True) -> None:
         self.model = model
@@ -73,6 +91,9 @@ class ModelRunner:
         self.graph_pool = None
         self.capture_stream = None
         self.graph_replays = 0
+        self.shape_graphs: OrderedDict[tuple, _DecodeGraph] = OrderedDict()
+        self.shapes_seen: OrderedDict[tuple, int] = OrderedDict()
+        self.shape_graph_replays = 0
         # The token last sampled for the request in each state slot; a step's token id of -1
         # reads it, so a sampled token can feed the next step without a trip to the host.
         self.last_token = torch.zeros(self.manager.slots.num_slots + 1, dtype=torch.int32, device=self.runtime.device)
@@ -118,6 +139,16 @@ class ModelRunner:
         bucket = min(width * page, -(-longest // self.KV_BUCKET) * self.KV_BUCKET)
         return (self.graph_batch(len(entries)), width, bucket, sampling is not None)
 
+    def _shape_key(self, entries, sampling) -> tuple | None:
+        """The exact shape of a step that is not decode-only (per entry: tokens, start, wanted places,
+        state slot), or None when such steps are not recorded."""
+        if not self.use_graphs or self.SHAPE_GRAPHS < 1 or len(entries) > self.SHAPE_GRAPH_MAX_ENTRIES:
+            return None
+        if sum(len(e.tokens) for e in entries) > self.SHAPE_GRAPH_MAX_TOKENS:
+            return None
+        return (tuple((len(e.tokens), self.manager.num_computed(e.key), tuple(e.want), self.manager.slot_of(e.key)) for e in entries),
+                sampling is not None)
+
     @staticmethod
     def graph_batch(count: int) -> int:
         """The batch size whose graph a decode step of `count` requests replays: itself up to 8,
@@ -157,13 +188,48 @@ class ModelRunner:
             logits, tokens = slot.logits[: len(entries)], None if slot.tokens is None else slot.tokens[: len(entries)]
             num_tokens = len(entries)
         else:
-            ctx = self.builder.build(entries, sampling)
-            logits, tokens = self._run(ctx)
-            num_tokens = ctx.num_tokens
+            logits, tokens, num_tokens = self._step_by_shape(entries, sampling) if key is None else self._eager(entries, sampling)
         for e in entries:
             self.manager.advance(e.key, len(e.tokens))
         wanted = [(e.key, int(w)) for e in entries for w in e.want]
         return StepOutput(logits, wanted, num_tokens, tokens)
+
+    def _eager(self, entries, sampling):
+        ctx = self.builder.build(entries, sampling)
+        logits, tokens = self._run(ctx)
+        return logits, tokens, ctx.num_tokens
+
+    def _step_by_shape(self, entries, sampling):
+        """A step that is not decode-only: eager the first time its shape is seen, recorded the
+        second time, replayed afterwards."""
+        key = self._shape_key(entries, sampling)
+        if key is None:
+            return self._eager(entries, sampling)
+        slot = self.shape_graphs.get(key)
+        if slot is None:
+            seen = self.shapes_seen.pop(key, 0)
+            if seen == 0:
+                self.shapes_seen[key] = 1
+                while len(self.shapes_seen) > self.SHAPES_REMEMBERED:
+                    self.shapes_seen.popitem(last=False)
+                return self._eager(entries, sampling)
+            ctx = self.builder.build(entries, sampling)
+            slot = _DecodeGraph(ctx.buffer)
+            self._capture(slot, ctx)
+            slot.num_tokens = ctx.num_tokens
+            self.shape_graphs[key] = slot
+            while len(self.shape_graphs) > self.SHAPE_GRAPHS:
+                self.shape_graphs.popitem(last=False)       # its memory goes back to the graphs' pool
+        else:
+            self.shape_graphs.move_to_end(key)
+            self.builder.build(entries, sampling, into=slot.buffer)
+            self.shape_graph_replays += 1
+        slot.graph.replay()
+        self.model.forward_pass_count += 1
+        ops = self.runtime.ops
+        if hasattr(ops, "launches"):
+            ops.launches += slot.launches
+        return slot.logits, slot.tokens, slot.num_tokens
 
     def _capture(self, slot: _DecodeGraph, ctx) -> None:
         """Records the step of `ctx` (whose integers lie in the buffer that replays will refill).

@@ -545,7 +545,8 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
             and weight.shape[1] == k and not isinstance(x, PendingSum) and _tensor_core_shape(x, weight, None, x.dtype)
             and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
         lib = _lib("gemm_tcgen05")
-        if lib.pae_linear_rotary_tcgen05_supports(head_dim):
+        # With so few output tiles that K is shared out over blocks, the sum of the planes rotates and writes.
+        if lib.pae_linear_rotary_tcgen05_supports(head_dim) and lib.pae_linear_tcgen05_plane_count(m, n, k) == 1:
             _need(x, "qkv_projection: x")
             _need(weight, "qkv_projection: weight")
             if bias is not None:

@@ -188,3 +188,66 @@ def test_command_line_generates_what_the_entry_point_generates(tmp_path):
         assert done.returncode == 0, done.stderr[-2000:]
         rows = [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
         assert [tuple(r["token_ids"]) for r in rows] == [tuple(w) for w in want], source
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_a_step_whose_shape_comes_again_is_recorded_and_replayed(tmp_path_factory, dtype_name):
+    """Steps that are not decode-only: the same shape (a portion of 70 tokens from position 0 beside
+    a portion of 33, then 21 more tokens of the first beside one decoded token of the second, in
+    the same state slots) comes four times with other tokens and other pages. The first time it runs eagerly, the second time
+    it is recorded, then replayed; every time the logits are the bits of a runner that records nothing."""
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_d", dtype_name)
+    engine = Engine.from_pretrained(folder, dtype_name)
+    rounds = [{name: helpers.random_tokens(raw["vocab_size"], n, 900 + 10 * r + i) for i, (name, n) in enumerate((("a", 91), ("b", 34)))}
+              for r in range(4)]
+
+    def run(use_graphs):
+        cache = engine.new_paged_cache(40, page, 4)
+        runner = engine.new_runner(cache)
+        runner.use_graphs = use_graphs and runner.use_graphs
+        got = []
+        for r, tokens in enumerate(rounds):
+            for name in tokens:
+                runner.begin_request(name)
+            if r == 2:        # other pages from here on: a request that stays holds some
+                runner.begin_request("keep")
+                assert cache.manager.reserve("keep", 3 * page).ok
+            for name in tokens:
+                assert cache.manager.reserve(name, len(tokens[name])).ok
+            first = runner.step([StepEntry("a", tokens["a"][:70], (0, 69)), StepEntry("b", tokens["b"][:33], (32,))])
+            got.append(first.logits.float().cpu().clone())
+            second = runner.step([StepEntry("a", tokens["a"][70:], (20,)), StepEntry("b", tokens["b"][33:], (0,))])
+            got.append(second.logits.float().cpu().clone())
+            for name in reversed(list(tokens)):      # the slot freed last is handed out first: "a" and "b" meet theirs again
+                runner.end_request(name)
+        return got, runner.shape_graph_replays, len(runner.shape_graphs)
+
+    recorded, replays, kept = run(True)
+    eager, none, nothing = run(False)
+    assert replays == 4 and kept == 2, "two shapes, each eager once, recorded once and replayed twice"
+    assert none == 0 and nothing == 0
+    for step, (a, b) in enumerate(zip(recorded, eager)):
+        assert torch.equal(a, b), f"step {step}"
+
+
+def test_recordings_by_shape_are_few(tmp_path_factory):
+    """The least recently used recording goes when more shapes come again than are kept."""
+    from paged_attention_engine_b200.engine.batch import StepEntry
+    from paged_attention_engine_b200.engine.llm import Engine
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_b", "bfloat16")
+    engine = Engine.from_pretrained(folder, "bfloat16")
+    cache = engine.new_paged_cache(16, page, 2)
+    runner = engine.new_runner(cache)
+    runner.SHAPE_GRAPHS = 2
+    for length in (5, 6, 7, 5, 6, 7, 7, 5):
+        runner.begin_request("x")
+        assert cache.manager.reserve("x", length).ok
+        runner.step([StepEntry("x", helpers.random_tokens(raw["vocab_size"], length, length), (length - 1,))])
+        runner.end_request("x")
+    keys = [key[0][0][0] for key in runner.shape_graphs]
+    # 5, 6 and 7 are recorded at their second coming, 5 goes when 7 comes; the third 7 is a replay; the third 5 starts over
+    assert keys == [6, 7] and runner.shape_graph_replays == 1, (keys, runner.shape_graph_replays)
