@@ -56,14 +56,17 @@ PAE_EXPORT int pae_paged_attention_decode(void* out, const void* qkv, const void
                              page_size, scale, window, slice_keys, max_slices, scratch, (cudaStream_t)stream);
 }
 
-// Requests that bring several tokens (and, unless skip_single, those that bring one).
+// Requests that bring several tokens (and, unless skip_single, those that bring one); with
+// `work_index` (device, `work_count` entries) only the requests it lists get blocks.
 PAE_EXPORT int pae_paged_attention_prefill(void* out, const void* qkv, const void* keys, const void* values,
                                            const int* block_table, int table_width, const int* q_start,
                                            const int* q_pos0, const int* kv_len, int seqs, int max_q_len, int heads,
                                            int kv_heads, int d, int page_size, float scale, int window,
-                                           int skip_single, void* stream) {
+                                           int skip_single, const int* work_index, int work_count, void* stream) {
   if (seqs == 0 || max_q_len == 0) return 0;
   if (int err = check_sizes("paged_attention_prefill", heads, kv_heads, d, page_size, seqs)) return err;
+  if (work_index != nullptr && (work_count < 1 || work_count > seqs))
+    return fail(2, "paged_attention_prefill: a list of %d requests to work on, of %d", work_count, seqs);
   PrefillParams p{};
   p.out = (__nv_bfloat16*)out;
   p.qkv = (const __nv_bfloat16*)qkv;
@@ -79,11 +82,13 @@ PAE_EXPORT int pae_paged_attention_prefill(void* out, const void* qkv, const voi
   p.page_size = page_size;
   p.window = window;
   p.skip_single = skip_single;
+  p.work_index = work_index;
   p.scale_log2 = scale * LOG2E;
   cudaStream_t s = (cudaStream_t)stream;
-  if (d == 32) return launch_prefill<32>(p, seqs, max_q_len, s);
-  if (d == 64) return launch_prefill<64>(p, seqs, max_q_len, s);
-  return launch_prefill<128>(p, seqs, max_q_len, s);
+  const int covered = work_index != nullptr ? work_count : seqs;       // grid z: the listed requests, or all
+  if (d == 32) return launch_prefill<32>(p, covered, max_q_len, s);
+  if (d == 64) return launch_prefill<64>(p, covered, max_q_len, s);
+  return launch_prefill<128>(p, covered, max_q_len, s);
 }
 
 PAE_DEFINE_LAST_ERROR()

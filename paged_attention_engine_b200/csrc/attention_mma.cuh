@@ -472,6 +472,7 @@ struct PrefillParams {
   const int* kv_len;
   int table_width, heads, kv_heads, page_size, window;
   int skip_single;              // requests of one token are left to the decode kernel
+  const int* work_index;        // the requests that this launch works on, one per grid z (null: request z)
   float scale_log2;
 };
 
@@ -480,7 +481,7 @@ __global__ void __launch_bounds__(128) prefill_kernel(const PrefillParams p) {
   dependent_launch_prologue();
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int h = blockIdx.y, b = p.work_index != nullptr ? p.work_index[blockIdx.z] : (int)blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   if (p.skip_single && q_count == 1) return;

@@ -60,6 +60,7 @@ struct Params {
   const int* q_pos0;
   const int* kv_len;
   int table_width, heads, kv_heads, page_size, window, skip_single;
+  const int* work_index;  // the requests that this launch works on, one per grid z (null: request z)
   float scale_log2;
   int* error;
 };
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(THREADS) prefill_tcgen05_kernel(const __grid_c
   // A cluster of `ranks` blocks shares one query tile of one head: each takes a run of its key
   // tiles, and the first block folds the others' outputs into its own at the end.
   const int ranks = SPLIT ? (int)cluster_size() : 1, rank = SPLIT ? (int)cluster_rank() : 0;
-  const int h = blockIdx.x / ranks, b = blockIdx.z;
+  const int h = blockIdx.x / ranks, b = p.work_index != nullptr ? p.work_index[blockIdx.z] : (int)blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   const int q_tiles = (q_count + BQ - 1) / BQ;
@@ -732,7 +733,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_tcgen05_paired_kernel(cons
   // ---- what this block works on (the same in every role) -------------------------------
   // The step's integers are read before the wait for the kernel before this one (they were on
   // the device before the step's first kernel began); q and this step's keys and values after it.
-  const int h = blockIdx.x, b = blockIdx.z;
+  const int h = blockIdx.x, b = p.work_index != nullptr ? p.work_index[blockIdx.z] : (int)blockIdx.z;
   const int first_token = p.q_start[b];
   const int q_count = p.q_start[b + 1] - first_token;
   const int q_tiles = (q_count + BQ - 1) / BQ;
@@ -1055,8 +1056,11 @@ int sm_count() {
 template <int D>
 int launch(const Params& p, const void* qkv, const void* keys, const void* values, int tokens, long long pages, int seqs,
            int working_seqs, int max_q_len, int max_kv_len, int form, int* chosen, cudaStream_t stream) {
-  dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, seqs);
-  // Blocks of requests that this launch leaves to the decode kernel return at once: they do not count.
+  // With a list of the requests to work on, the grid covers those only. Without one it covers
+  // all, and the blocks of requests that are left to the decode kernel return at once; they do
+  // not count below, but each still costs its launch (one block of 200 KB per SM at a time: 65
+  // requests of which one brings a portion took 75 us where that portion needs 15).
+  dim3 grid(p.heads, (max_q_len + BQ - 1) / BQ, p.work_index != nullptr ? working_seqs : seqs);
   const long long blocks = (long long)grid.x * grid.y * working_seqs;
   const bool use_paired = form == 2 || (form == 0 && blocks >= 2LL * sm_count());
   unsigned ranks = 1;
@@ -1106,14 +1110,16 @@ PAE_EXPORT int pae_attention_tcgen05_supports(int heads, int kv_heads, int d, in
 }
 
 // Attention of every request that brings more than one token (or every request, unless
-// skip_single; `singles` is how many bring one, -1 when the caller does not know). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests); `chosen` (a host pointer, or null) receives the blocks per query tile of this launch: 1 without clusters, 0 for the paired kernel. qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
+// skip_single; `singles` is how many bring one, -1 when the caller does not know). form 0 picks the kernel by the size of the launch, 1 and 2 name it (tests); `chosen` (a host pointer, or null) receives the blocks per query tile of this launch: 1 without clusters, 0 for the paired kernel. `work_index` (device, or null) lists the `work_count` requests that the launch is to cover, in place of all `seqs`. qkv [tokens, heads + 2 kv_heads, d]; keys, values [pages, kv_heads, page_size, d].
 PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, const void* keys, const void* values,
                                                    long long pages, const int* block_table, int table_width,
                                                    const int* q_start, const int* q_pos0, const int* kv_len, int tokens,
                                                    int seqs, int max_q_len, int max_kv_len, int heads, int kv_heads, int d,
                                                    int page_size, float scale, int window, int skip_single, int singles, int form, int* chosen,
-                                                   int* error, void* stream) {
+                                                   const int* work_index, int work_count, int* error, void* stream) {
   if (seqs == 0 || max_q_len == 0 || tokens == 0) return 0;
+  if (work_index != nullptr && (work_count < 1 || work_count > seqs))
+    return fail(2, "paged_attention_tcgen05: a list of %d requests to work on, of %d", work_count, seqs);
   if (!pae_attention_tcgen05_supports(heads, kv_heads, d, page_size))
     return fail(2, "paged_attention_tcgen05: head_dim %d with pages of %d is not taken (64 or 128; 16, 32, 64 or 128)", d, page_size);
   if (heads > 65535 || seqs > 65535) return fail(3, "paged_attention_tcgen05: %d heads x %d requests exceed one launch", heads, seqs);
@@ -1134,7 +1140,8 @@ PAE_EXPORT int pae_paged_attention_prefill_tcgen05(void* out, const void* qkv, c
   p.scale_log2 = scale * LOG2E;
   p.error = error;
   cudaStream_t s = (cudaStream_t)stream;
-  const int working_seqs = skip_single && singles > 0 && singles < seqs ? seqs - singles : seqs;
+  p.work_index = work_index;
+  const int working_seqs = work_index != nullptr ? work_count : (skip_single && singles > 0 && singles < seqs ? seqs - singles : seqs);
   if (d == 64) return launch<64>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, chosen, s);
   return launch<128>(p, qkv, keys, values, tokens, pages, seqs, working_seqs, max_q_len, max_kv_len, form, chosen, s);
 }

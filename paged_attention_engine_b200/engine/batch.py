@@ -56,6 +56,9 @@ class StepContext:
     max_q_len: int
     max_kv_len: int
     num_single: int               # entries that bring exactly one token
+    # int32 [entries - num_single]: the entries that bring more than one token, in their order; None
+    # when all or none do. Attention's portion kernels then launch blocks for these entries only.
+    multi_index: torch.Tensor | None
     wants_every_token: bool       # logit_rows is 0, 1, ..., tokens - 1: no gather is needed
     groups: list[GroupStep]
     # Host copies, for parts (and tests) that plan on the host.
@@ -230,7 +233,12 @@ class BatchBuilder:
         num_groups = len(manager.groups)
         if sampling is not None and len(sampling) != len(rows) - pads:
             raise ValueError(f"{len(sampling)} sampling rows for {len(rows) - pads} wanted places")
+        multi = [i for i, n in enumerate(q_lens) if n > 1]
+        if len(multi) in (0, b):
+            multi = []
         sizes = [total, total, total, b + 1, b, b, b, len(rows)] + [b * width, total] * num_groups
+        multi_at = len(sizes)
+        sizes.append(len(multi))
         first_sampling = len(sizes)
         if sampling is not None:
             sizes += [len(rows)] * 5
@@ -248,6 +256,7 @@ class BatchBuilder:
         put(5, kv_len)
         put(6, slots_of)
         put(7, rows)
+        put(multi_at, multi)
         page_index = positions // page
         offset = positions - page_index * page
         for g in range(num_groups):
@@ -292,7 +301,7 @@ class BatchBuilder:
             token_ids=part(0), positions=part(1), seq_index=part(2), q_start=part(3), q_pos0=part(4),
             kv_len=part(5), state_slot=part(6), logit_rows=part(7),
             max_q_len=max(q_lens), max_kv_len=planned_kv,
-            num_single=sum(1 for n in q_lens if n == 1), wants_every_token=len(rows) == total and rows == list(range(total)), groups=groups,
+            num_single=sum(1 for n in q_lens if n == 1), multi_index=part(multi_at) if multi else None, wants_every_token=len(rows) == total and rows == list(range(total)), groups=groups,
             host_q_lens=list(q_lens), host_q_pos0=list(pos0), host_state_slots=list(slots_of),
             sampling=sampling_parts, buffer=dev,
         )

@@ -618,10 +618,13 @@ def _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len,
 
 def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads, head_dim,
                     page_size, max_q_len, max_kv_len, scale, window, num_single=None, form: int = 0,
-                    info: dict | None = None) -> torch.Tensor:
+                    info: dict | None = None, multi_index: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages. `num_single` is the number
     of requests that bring exactly one token when the caller knows it (it decides which kernels
-    are launched; None launches whatever may be needed). `form` 0 lets the tcgen05 attention pick
+    are launched; None launches whatever may be needed). `multi_index` (int32, device) lists the
+    requests that bring more than one token when some do and some do not: the portion kernels
+    then launch blocks for those only (a step of 64 decoding requests and one prompt portion
+    otherwise launches 65 requests' worth of blocks, 64 of which return at once but not for free). `form` 0 lets the tcgen05 attention pick
     its kernel by the size of the launch (two blocks of 64-key tiles per SM when there are that
     many blocks, else one block of 128-key tiles, its keys shared out over a cluster when the
     blocks are few); 1, 2, 4, 8, 16 name the kernel (tests). `info`, when given, receives which
@@ -640,6 +643,12 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
         lib = _lib("attention_mma")
         mma_ok = bool(lib.pae_attention_mma_supports(num_heads, num_kv_heads, head_dim, page_size))
         singles = num_single if num_single is not None else (seqs if max_q_len == 1 else -1)
+        # The requests that bring more than one token, when the caller lists them and the decode kernel takes the others.
+        listed = multi_index if (multi_index is not None and mma_ok and singles > 0) else None
+        if listed is not None:
+            _need(listed, "paged_attention: multi_index", torch.int32)
+            if listed.numel() != seqs - singles:
+                raise KernelError(f"paged_attention: {listed.numel()} requests listed, {seqs - singles} bring more than one token")
         # Portions of 64 tokens and more: both products on tcgen05, one thread per query row.
         if use_tcgen05_attention and max_q_len >= TCGEN05_ATTENTION_MIN_TOKENS:
             tc5 = _lib("attention_tcgen05")
@@ -652,7 +661,8 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
                     block_table.shape[1], _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), tokens, seqs,
                     max_q_len, max_kv_len, num_heads, num_kv_heads, head_dim, page_size,
                     scale, window, (1 if decode_after else 0), singles, form,
-                    ctypes.byref(chosen), _ptr(_error_flag(qkv.device)), _stream()))
+                    ctypes.byref(chosen), _ptr(listed), (listed.numel() if listed is not None else 0),
+                    _ptr(_error_flag(qkv.device)), _stream()))
                 if info is not None:
                     info.update(kernel="tcgen05", cluster=chosen.value)
                 if decode_after:
@@ -668,7 +678,7 @@ def paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num
                     _ptr(out), _ptr(qkv), _ptr(keys), _ptr(values), _ptr(block_table), block_table.shape[1],
                     _ptr(q_start), _ptr(q_pos0), _ptr(kv_len), seqs, max_q_len, num_heads,
                     num_kv_heads, head_dim, page_size, scale, window,
-                    1, _stream()))
+                    1, _ptr(listed), (listed.numel() if listed is not None else 0), _stream()))
             if singles != 0:
                 _decode_attention(lib, out, qkv, keys, values, block_table, q_start, kv_len, seqs, singles, num_heads,
                                   num_kv_heads, head_dim, page_size, max_kv_len, scale, window)

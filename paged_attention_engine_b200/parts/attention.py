@@ -85,5 +85,6 @@ class GQAAttention(Part):
             qkv, cache.keys, cache.values, group.block_table, ctx.q_start, ctx.q_pos0, ctx.kv_len,
             self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size,
             ctx.max_q_len, ctx.max_kv_len, self.scale, self.window, num_single=ctx.num_single,
+            multi_index=getattr(ctx, "multi_index", None),
         )
         return ops.linear(out, self.o_weight, None, residual)

@@ -29,7 +29,7 @@ class FaultyOps:
         return getattr(self.real, name)
 
     def paged_attention(self, qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads, num_kv_heads,
-                        head_dim, page_size, max_q_len, max_kv_len, scale, window, num_single=None):
+                        head_dim, page_size, max_q_len, max_kv_len, scale, window, num_single=None, multi_index=None):
         layer = self.calls % self.layers
         self.calls += 1
         if layer == self.layer:
@@ -47,7 +47,7 @@ class FaultyOps:
                 self.faults_made += 1
         return self.real.paged_attention(qkv, keys, values, block_table, q_start, q_pos0, kv_len, num_heads,
                                          num_kv_heads, head_dim, page_size, max_q_len, max_kv_len, scale, window,
-                                         num_single=num_single)
+                                         num_single=num_single, multi_index=multi_index)
 
 
 class RecordingOps:

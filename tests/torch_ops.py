@@ -72,7 +72,7 @@ def rotary_qk_cache_write(qkv, table, slots, keys, values, num_heads, num_kv_hea
 
 def paged_attention(
     qkv, keys, values, block_table, q_start, q_pos0, kv_len,
-    num_heads, num_kv_heads, head_dim, page_size, max_q_len, max_kv_len, scale, window, num_single=None,
+    num_heads, num_kv_heads, head_dim, page_size, max_q_len, max_kv_len, scale, window, num_single=None, multi_index=None,
 ):
     tokens = qkv.shape[0]
     q_all = qkv.view(tokens, num_heads + 2 * num_kv_heads, head_dim)[:, :num_heads]
