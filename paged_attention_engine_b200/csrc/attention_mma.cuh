@@ -352,11 +352,13 @@ __global__ void __launch_bounds__(SLICE_WARPS * 32) decode_slices_kernel(const D
 // One block of four warps per (request, head). Everything the block needs is asked for before
 // anything is waited for: a thread's slice maxima and sums, and the partial outputs of the
 // slices its warp folds (warp w takes slices w, w + 4, ...; a lane owns D / 32 neighbouring
-// dimensions), sixteen slices per warp at a time. The weights are then worked out once into
+// dimensions), twenty-four slices per warp at a time (96 in all: the most that a step of few
+// requests is cut into; with sixteen, the 74 slices of batch 8 at context 4,096 cost a warp a
+// further trip to memory). The weights are then worked out once into
 // shared memory, each warp folds its slices in their order, and the warps' sums are added in
 // the order of the warps, so the result does not depend on timing.
 constexpr int MERGE_WARPS = 4;
-constexpr int MERGE_DEPTH = 16;      // slices per warp whose partial outputs are in registers at one time
+constexpr int MERGE_DEPTH = 24;      // slices per warp whose partial outputs are in registers at one time
 
 template <int D>
 __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_slices_kernel(
@@ -440,7 +442,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_slices_kernel(
       for (int j = 0; j < PER_LANE; ++j) acc[j] += part[i][j] * w;
     }
   }
-  for (int s = warp + MERGE_DEPTH * MERGE_WARPS; s < slices; s += MERGE_WARPS) {     // more than 64 slices
+  for (int s = warp + MERGE_DEPTH * MERGE_WARPS; s < slices; s += MERGE_WARPS) {     // more than 96 slices
     const float w = weights[s];
     const float* from = part_out + (at + s) * D + lane * PER_LANE;
 #pragma unroll
