@@ -118,3 +118,31 @@ def test_temperature_sampling_does_not_depend_on_the_batch(tmp_path):
     greedy = LLM(engine, num_blocks=64, block_size=page)
     greedy.add_request(Request("t2", prompts["t2"], 6))
     assert greedy.run_to_completion()["t2"] != together["t2"]
+
+
+def test_the_step_lists_the_requests_that_bring_more_than_one_token():
+    """`multi_index`: the entries that bring a portion, in their order, when some entries do and some
+    bring one token; None when all or none do (the portion kernels then cover every request)."""
+    from paged_attention_engine_b200.cache.manager import CacheManager, KVGroupSpec
+    from paged_attention_engine_b200.engine.batch import BatchBuilder, StepEntry
+
+    manager = CacheManager((KVGroupSpec(num_kv_heads=1, head_dim=16, window=0, entries=(0,)),), 32, 8, 8)
+    builder = BatchBuilder(manager, torch_ops, torch.float32, "cpu", 100)
+
+    def build(lengths):
+        entries = []
+        for i, n in enumerate(lengths):
+            manager.create_request(i)
+            assert manager.reserve(i, n).ok
+            entries.append(StepEntry(i, list(range(1, n + 1)), (n - 1,)))
+        ctx = builder.build(entries)
+        for i in range(len(lengths)):
+            manager.free_request(i)
+        return ctx
+
+    mixed = build([1, 5, 1, 1, 9, 2, 1])
+    assert mixed.multi_index.tolist() == [1, 4, 5] and mixed.num_single == 4
+    assert build([1, 1, 1]).multi_index is None
+    assert build([4, 2]).multi_index is None
+    # the other integers lie where they did
+    assert mixed.q_start.tolist() == [0, 1, 6, 7, 8, 17, 19, 20] and mixed.logit_rows.tolist() == [0, 5, 6, 7, 16, 18, 19]

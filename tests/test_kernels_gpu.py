@@ -320,6 +320,37 @@ def test_tcgen05_prefill_attention(ops, heads, kv_heads, d, page, window, form, 
     assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -6 * float(other.float().abs().max())
 
 
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [(12, 2, 128, 16, 0), (4, 4, 64, 32, 90)])
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_portion_kernels_launched_for_the_listed_requests_only(ops, heads, kv_heads, d, page, window, kernel):
+    """Many requests that bring one token beside a few portions: with the list of those that bring
+    more than one, the portion kernels launch blocks for them only; the result is the bits of a
+    launch that covers every request and lets the blocks of the others return. A list of the wrong
+    length is refused."""
+    gen = torch.Generator().manual_seed(41)
+    q_lens = [1] * 9 + [130] + [1] * 7 + [66, 1, 1, 2] + [1] * 5
+    pos0 = [int(v) for v in torch.randint(0, 600, (len(q_lens),), generator=gen)]
+    tensors, kv_lens = _paged_case(gen, q_lens, pos0, heads, kv_heads, d, page, torch.bfloat16)
+    args = dict(num_heads=heads, num_kv_heads=kv_heads, head_dim=d, page_size=page, max_q_len=max(q_lens),
+                max_kv_len=max(kv_lens), scale=d ** -0.5, window=window, num_single=q_lens.count(1))
+    multi = torch.tensor([i for i, n in enumerate(q_lens) if n > 1], dtype=torch.int32).cuda()
+    want = ref.paged_attention(*tensors, **{k: v for k, v in args.items() if k != "num_single"})
+    on_device = [t.cuda() for t in tensors]
+    ops.use_tcgen05_attention = kernel == "tcgen05"
+    try:
+        info = {}
+        listed = ops.paged_attention(*on_device, **args, multi_index=multi, info=info)
+        everyone = ops.paged_attention(*on_device, **args)
+        assert info["kernel"] == kernel
+        with pytest.raises(ops.KernelError, match="requests listed"):
+            ops.paged_attention(*on_device, **args, multi_index=multi[:2])
+    finally:
+        ops.use_tcgen05_attention = True
+    ops.check_device_errors()
+    assert torch.equal(listed, everyone)
+    _close(listed, want, torch.bfloat16, scale=2.0)
+
+
 @pytest.mark.parametrize("heads,kv_heads,d,page,window", [(4, 2, 128, 16, 100), (6, 3, 64, 32, 70), (2, 1, 128, 16, 257), (4, 4, 64, 16, 33)])
 @pytest.mark.parametrize("form", ["mma", 1, 2, 0])
 def test_windowed_attention_over_a_table_with_released_pages(ops, heads, kv_heads, d, page, window, form):
