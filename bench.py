@@ -246,6 +246,99 @@ def time_prefill(engine, torch, repeats: int = PASSES, tokens: int = PREFILL_TOK
     return summary(times)
 
 
+def time_products(model: dict, tokens: int, torch, peak: dict, copies: int = 28) -> list[dict]:
+    """The four matrix products of a decoder layer for a step of `tokens` tokens, with what a step
+    runs around them (norm before, rotation and page write, SiLU x up, residual after), each
+    `copies` times in a row on weights of their own (nothing is found in L2), recorded into a
+    CUDA graph and replayed: microseconds per product, for the kernels the engine picks and for
+    the tcgen05 products with their summing kernels alone."""
+    from paged_attention_engine_b200.kernels import ops
+
+    dev = "cuda:0"
+    hidden, inter = model["hidden_size"], model["intermediate_size"]
+    heads, kv_heads, d = model["num_attention_heads"], model["num_key_value_heads"], model["head_dim"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def bf(*shape, std=1.0):
+        return (torch.randn(*shape, device=dev, generator=gen) * std).to(torch.bfloat16)
+
+    x, xi, res, attn = bf(tokens, hidden), bf(tokens, inter, std=0.3), bf(tokens, hidden), bf(tokens, heads * d)
+    gamma = torch.rand(hidden, device=dev, generator=gen) + 0.5
+    nq = (heads + 2 * kv_heads) * d
+    wq = [bf(nq, hidden, std=0.02) for _ in range(copies)]
+    bq = torch.randn(nq, device=dev, generator=gen)
+    wo = [bf(hidden, heads * d, std=0.02) for _ in range(copies)]
+    wgu = [ops.interleave_gate_up(bf(inter, hidden, std=0.02), bf(inter, hidden, std=0.02)) for _ in range(copies)]
+    wd = [bf(hidden, inter, std=0.02) for _ in range(copies)]
+    table = torch.randn(tokens, d, device=dev, generator=gen)
+    page = BLOCK_SIZE
+    keys = torch.zeros(tokens // page + 2, kv_heads, page, d, dtype=torch.bfloat16, device=dev)
+    values = torch.zeros_like(keys)
+    slots = torch.arange(tokens, dtype=torch.int32, device=dev)
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def qkv():
+        for w in wq:
+            ops.materialized(ops.qkv_projection(ops.rms_norm(x, gamma, 1e-6), w, bq, table, slots, keys, values, heads, kv_heads, d, page))
+
+    def o():
+        for w in wo:      # the sum of a split product is part of the norm that follows it: run that norm, too
+            ops.materialized(ops.rms_norm(ops.linear(attn, w, residual=res), gamma, 1e-6))
+
+    def gate_up():
+        for w in wgu:
+            ops.materialized(ops.linear_swiglu(ops.rms_norm(x, gamma, 1e-6), w))
+
+    def down():
+        for w in wd:
+            ops.materialized(ops.linear(xi, w, residual=res))
+
+    def layer():
+        for i in range(copies):
+            ops.qkv_projection(ops.rms_norm(x, gamma, 1e-6), wq[i], bq, table, slots, keys, values, heads, kv_heads, d, page)
+            r = ops.linear(attn, wo[i], residual=res)
+            a = ops.linear_swiglu(ops.rms_norm(r, gamma, 1e-6), wgu[i])
+            ops.materialized(ops.linear(a, wd[i], residual=r))
+
+    def replayed(fn) -> float:
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            fn()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(7):
+            flush.zero_()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end) * 1e3 / copies)
+        return statistics.median(times)
+
+    groups = (("q|k|v", qkv, nq * hidden), ("o", o, hidden * heads * d), ("gate|up", gate_up, 2 * inter * hidden), ("down", down, hidden * inter),
+              ("the four in a row", layer, nq * hidden + hidden * heads * d + 3 * inter * hidden))
+    rows = []
+    for name, fn, weights in groups:
+        row = {"only": "products", "product": name, "tokens": tokens, "weight_mb": round(weights * 2 / 1e6, 1),
+               "us_at_hbm_peak": round(weights * 2 / peak["hbm_gbs"] / 1e3, 2)}
+        for label, few in (("us", True), ("us_tcgen05_chain", False)):
+            ops.use_few_token_products = few
+            try:
+                row[label] = round(replayed(fn), 2)
+            finally:
+                ops.use_few_token_products = True
+        rows.append(row)
+    return rows
+
+
 def time_end_to_end(engine, batch: int, steps: int, warmup: int, torch):
     """The same decode steps through the Python entry point: requests are added with host
     token ids, prefilled by the scheduler, and every timed `step()` copies its inputs to the
@@ -565,7 +658,7 @@ def main() -> int:
                         help="layer sizes for --only decode / prefill (the headline line is always the 1.5B shape)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length for --only decode")
     parser.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="prompt length for --only prefill")
-    parser.add_argument("--only", choices=("all", "decode", "prefill", "stream7b", "pressure32b"), default="all",
+    parser.add_argument("--only", choices=("all", "decode", "prefill", "products", "stream7b", "pressure32b"), default="all",
                         help="time one part only (for profiling); the JSON line then holds that part alone")
     args = parser.parse_args()
 
@@ -593,6 +686,10 @@ def main() -> int:
         return 0
     if args.only == "pressure32b":
         print(json.dumps(pressure_32b(torch, args.layers_32b)))
+        return 0
+    if args.only == "products":
+        for row in time_products({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape], args.batch, torch, peak):
+            print(json.dumps(row))
         return 0
 
     model = dict({"1.5b": MODEL, "7b": MODEL_7B, "32b": MODEL_32B}[args.shape] if args.only != "all" else MODEL)
