@@ -19,19 +19,21 @@
 //             epilogue = scale, rounding, SiLU(gate) * up.
 //   o, down   16 neighbouring rows; epilogue = + residual, rounding.
 //
-// Weights: every warp runs a ring of its own, filled by TMA (two boxes of 8 rows x 64 of K per
-// stage, 128-byte swizzle, which is the layout ldmatrix wants) and watched through one mbarrier
-// per stage; the warp that reads a stage is the warp that asks for the next chunk into it, so the
-// main loop has no block-wide barrier. The first stages are asked for BEFORE the wait for the
-// kernel before this one (weights were written when the model was loaded), so they stream while
-// that kernel finishes. Plain 16-byte cp.async copies of the same chunks kept too little on the
-// way per SM: 1.4 to 2.4 TB/s where the TMA ring streams.
+// Weights: every warp runs a ring of its own, filled by TMA and watched through one mbarrier
+// per stage. A stage is two to four neighbouring chunks of 64 of K: two copies of 8 rows x 64 x
+// chunks each (the lower and the upper eight MMA rows), 128-byte swizzle, which is the layout
+// ldmatrix wants. The warp that reads a stage is the warp that asks for the next one into it, so
+// the main loop has no block-wide barrier. The first stages are asked for BEFORE the wait for
+// the kernel before this one (weights were written when the model was loaded), so they stream
+// while that kernel finishes. Plain 16-byte cp.async copies of the same chunks kept too little
+// on the way per SM: 1.4 to 2.4 TB/s where the TMA ring streams.
 //
 // Activations. Where the input is a norm's (q|k|v, gate|up), the block first builds, once, the
 // whole operand in shared memory: x * norm weight in float32, rounded to bfloat16, already in the
 // order of the MMA's B fragments (one 8-byte load per lane and k-step), and the tokens'
 // rsqrt(mean x^2 + eps). Where it is not (o, down), the warps' K ranges differ and the
-// activations' chunk [tokens x 64] comes through the ring beside the weights' chunk.
+// activations' chunks [tokens x 64] come through the ring beside the weights' chunks. What the
+// epilogue adds (bias, angles and slots, the residual) is asked for before the main loop.
 //
 // Sizes: K a multiple of 64, at most 16 tokens, head_dim a multiple of 16, and shared memory
 // for the ring and a normed operand. Everything else is refused here and runs on the tcgen05
