@@ -580,11 +580,13 @@ def decode_slicing(seqs: int, kv_heads: int, max_kv_len: int, most: int | None =
     keep all blocks in that one wave (a second, partly filled wave costs as much as a full
     one), at most `most`, each of at least 32 keys in steps of 16. A warp walks its slice one
     trip to memory after the other, so short slices are what makes few requests fast: up to 96
-    while a slice keeps 64 keys (batch 1 at context 4,096: 0.940 -> 0.915 ms a step, batch 8:
-    1.032 -> 1.024); beyond that the merge's share grows and 64 slices are the most (batch 8 at
-    context 16,384: 1.457 ms against 1.474 with 74)."""
+    for contexts of up to 6,144 keys (batch 1 at context 4,096: 0.940 -> 0.915 ms a step, batch 8:
+    1.032 -> 1.024), beyond that up to 192 of at least 64 keys (batch 1 at context 32,768: 1.72 ms
+    with 64 slices, 1.43 with 96, 1.24 with 192, 1.21 with 256, 1.25 with 384; batch 4 at 16,384:
+    1.33, 1.20, 1.21; eight requests and more fill the wave with fewer slices anyway). The merge
+    holds 96 slices' partial outputs in registers and walks the rest one by one."""
     if most is None:
-        most = 96 if max_kv_len <= 96 * 64 else 64
+        most = 96 if max_kv_len <= 96 * 64 else min(192, max_kv_len // 64)
     pairs = max(1, seqs * kv_heads)
     blocks_per_pair = max(1, wave_blocks // pairs)
     wanted = max(1, min(most, slices_per_block * blocks_per_pair))
