@@ -328,6 +328,11 @@ use_tensor_cores = True
 # Whether a split-K product is summed inside the kernel that consumes it (tests compare both).
 fuse_split_sums = True
 SWAPPED_MAX_TOKENS = 64
+# gate|up takes the many-token kernel (SiLU x up in its epilogue, no split of K, tiles of 128 tokens)
+# from 33 tokens on: at 64 tokens 16.8 against 21.9 us at the 1536-wide sizes and 52.2 against
+# 61.1 us at the 3584-wide ones; at 32 tokens 18.7 against 17.6 and 51.6 against 53.4, below that the
+# swapped product and the kernel that adds its two splits are faster.
+SWIGLU_SWAPPED_MAX_TOKENS = 32
 
 _error_flags: dict[int, torch.Tensor] = {}
 
@@ -750,7 +755,7 @@ def linear_swiglu(x, weight) -> torch.Tensor:
     x = materialized(x)
     m, k = x.shape
     n = weight.shape[0]
-    if (m > SWAPPED_MAX_TOKENS and n >= 256 and n % 32 == 0 and _tensor_core_shape(x, weight, None, x.dtype)
+    if (m > SWIGLU_SWAPPED_MAX_TOKENS and n >= 256 and n % 32 == 0 and _tensor_core_shape(x, weight, None, x.dtype)
             and weight.shape[1] == k):
         _need(x, "linear_swiglu: x")
         _need(weight, "linear_swiglu: weight")
