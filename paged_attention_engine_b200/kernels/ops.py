@@ -328,6 +328,17 @@ use_tensor_cores = True
 # Whether a split-K product is summed inside the kernel that consumes it (tests compare both).
 fuse_split_sums = True
 SWAPPED_MAX_TOKENS = 64
+# ... and up to this many where K is long (2,048 and more): the swapped product's blocks then
+# have enough of K each, and it stays ahead of the many-token kernel with its K shared out in
+# planes (128 tokens at the 3584-wide sizes: q|k|v 19.8 against 22.5 us, o 16.3 against 19.2; down of
+# the 1536-wide sizes, K = 8960: 14.0 against 16.3; its q|k|v and o, K = 1536: 14.7 and 10.5 against 12.4 and 9.7).
+SWAPPED_MAX_TOKENS_LONG_K = 128
+SWAPPED_LONG_K = 2048
+
+
+def _swapped(m: int, k: int) -> bool:
+    """Whether a product of m tokens over K takes the swapped split-K kernel."""
+    return m <= SWAPPED_MAX_TOKENS or (m <= SWAPPED_MAX_TOKENS_LONG_K and k >= SWAPPED_LONG_K)
 # gate|up takes the many-token kernel (SiLU x up in its epilogue, no split of K, tiles of 128 tokens)
 # from 33 tokens on: at 64 tokens 16.8 against 21.9 us at the 1536-wide sizes and 52.2 against
 # 61.1 us at the 3584-wide ones; at 32 tokens 18.7 against 17.6 and 51.6 against 53.4, below that the
@@ -436,7 +447,7 @@ def _linear_tensor_cores(x, weight, bias, residual, out_dtype, m, n, k) -> torch
     lib = _lib("gemm_tcgen05")
     flag = _error_flag(x.device)
     out_f32 = (1 if out_dtype == torch.float32 else 0)
-    if m <= SWAPPED_MAX_TOKENS:
+    if _swapped(m, k):
         # Few tokens: weight rows fill the MMA's 128 rows, K is split, partial sums are
         # float32 scratch that the reduction (or nothing, for one split) turns into the output.
         splits = lib.pae_linear_swapped_splits(n, k)
@@ -546,7 +557,7 @@ def qkv_projection(x, weight, bias, table, slots, keys, values, num_heads, num_k
             num_kv_heads, head_dim, page_size, k, _ptr(_error_flag(source.device)), _stream()))
         return out
     x = materialized(x)
-    if (fuse_qkv_epilogue and m > SWAPPED_MAX_TOKENS and n >= 256 and n == (num_heads + 2 * num_kv_heads) * head_dim
+    if (fuse_qkv_epilogue and not _swapped(m, k) and n >= 256 and n == (num_heads + 2 * num_kv_heads) * head_dim
             and weight.shape[1] == k and not isinstance(x, PendingSum) and _tensor_core_shape(x, weight, None, x.dtype)
             and (slots is None or (keys.dtype == torch.bfloat16 and values.dtype == torch.bfloat16))):
         lib = _lib("gemm_tcgen05")

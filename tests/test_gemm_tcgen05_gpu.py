@@ -98,11 +98,21 @@ def test_few_output_tiles_and_a_long_k_share_k_over_blocks(ops, m, n, k, extras)
     assert lib.pae_linear_tcgen05_plane_count(ctypes.c_int(m), ctypes.c_int(n), ctypes.c_int(k)) == planes
     x = _rand((m, k), 1)
     w = _rand((n, k), 2, 0.05)
-    pending = ops.linear(x, w)
-    assert isinstance(pending, ops.PendingSum) == (planes > 1)
-    if planes > 1:
-        assert tuple(pending.partial.shape) == (planes, m, n)
-    _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
+    # Up to 128 tokens over a K of 2,048 and more stay with the swapped product (its splits, not planes);
+    # the many-token kernel and its plane rule are asked for those sizes all the same.
+    for long_k_limit in (ops.SWAPPED_MAX_TOKENS_LONG_K, ops.SWAPPED_MAX_TOKENS):
+        ops.SWAPPED_MAX_TOKENS_LONG_K = long_k_limit
+        try:
+            pending = ops.linear(x, w)
+            if ops._swapped(m, k):
+                assert tuple(pending.partial.shape) == (lib.pae_linear_swapped_splits(n, k), m, n)
+            else:
+                assert isinstance(pending, ops.PendingSum) == (planes > 1)
+                if planes > 1:
+                    assert tuple(pending.partial.shape) == (planes, m, n)
+            _check(ops, m, n, k, bias=extras[0], residual=extras[1], out_dtype=torch.bfloat16)
+        finally:
+            ops.SWAPPED_MAX_TOKENS_LONG_K = 128
 
 
 def test_a_wait_that_runs_out_is_reported_and_the_next_call_is_right(ops):
