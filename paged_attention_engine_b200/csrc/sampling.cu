@@ -31,6 +31,20 @@ __device__ __forceinline__ bool better(float v, int i, float best, int best_i) {
 constexpr int THREADS = 512;
 constexpr int CHUNK = 4096;      // vocabulary entries per block of the first stage
 
+// Where a sampled token also goes so that the next step's embedding finds it on the device:
+// last_token[state_slot[seq_index[logit_rows[r]]]] (engine/scheduler.py:610 reads every token
+// back before it goes on; here only the host's copy waits). All null: nowhere.
+struct Scatter {
+  int* last_token;
+  const int* logit_rows;
+  const int* seq_index;
+  const int* state_slot;
+};
+__device__ __forceinline__ void keep(int* tokens, const Scatter& to, int r, int token) {
+  tokens[r] = token;
+  if (to.last_token != nullptr) to.last_token[to.state_slot[to.seq_index[to.logit_rows[r]]]] = token;
+}
+
 struct Best {
   float value;
   int index;
@@ -76,7 +90,7 @@ __global__ void __launch_bounds__(THREADS) sample_chunks_kernel(int* __restrict_
                                                                 const float* __restrict__ temperature,
                                                                 const int* __restrict__ seed_lo, const int* __restrict__ seed_hi,
                                                                 const int* __restrict__ request_key,
-                                                                const int* __restrict__ output_index, int vocab, int chunks) {
+                                                                const int* __restrict__ output_index, int vocab, int chunks, const Scatter to) {
   dependent_launch_prologue();
   __shared__ float best_v[THREADS / 32];
   __shared__ int best_i[THREADS / 32];
@@ -109,7 +123,7 @@ __global__ void __launch_bounds__(THREADS) sample_chunks_kernel(int* __restrict_
   const Best best = block_best(v_best, i_best, best_v, best_i);
   if (threadIdx.x == 0) {
     if (chunks == 1) {
-      tokens[r] = best.index == 0x7fffffff ? 0 : best.index;
+      keep(tokens, to, r, best.index == 0x7fffffff ? 0 : best.index);
     } else {
       chunk_value[(size_t)r * chunks + chunk] = best.value;
       chunk_index[(size_t)r * chunks + chunk] = best.index;
@@ -119,7 +133,7 @@ __global__ void __launch_bounds__(THREADS) sample_chunks_kernel(int* __restrict_
 
 // Second stage: the best of a row's chunks (ties to the lowest index, as within a chunk).
 __global__ void sample_rows_kernel(int* __restrict__ tokens, const float* __restrict__ chunk_value,
-                                   const int* __restrict__ chunk_index, int chunks) {
+                                   const int* __restrict__ chunk_index, int chunks, const Scatter to) {
   dependent_launch_prologue();
   __shared__ float best_v[4];
   __shared__ int best_i[4];
@@ -135,7 +149,7 @@ __global__ void sample_rows_kernel(int* __restrict__ tokens, const float* __rest
     }
   }
   const Best best = block_best(v_best, i_best, best_v, best_i);
-  if (threadIdx.x == 0) tokens[r] = best.index == 0x7fffffff ? 0 : best.index;
+  if (threadIdx.x == 0) keep(tokens, to, r, best.index == 0x7fffffff ? 0 : best.index);
 }
 
 }  // namespace
@@ -149,22 +163,28 @@ PAE_EXPORT long long pae_sample_scratch_words(int rows, int vocab) {
 // tokens int32 [rows]; logits float32 [rows, vocab]; per row: temperature (float32),
 // the two halves of the 64-bit seed, the request's key and the index of the output token.
 // `scratch` holds pae_sample_scratch_words(rows, vocab) words (may be null when that is 0).
+// With `last_token` (and the step's logit_rows, seq_index, state_slot) the token of row r is also
+// written to last_token[state_slot[seq_index[logit_rows[r]]]]; null leaves that to the caller.
 PAE_EXPORT int pae_sample(int* tokens, const float* logits, const float* temperature, const int* seed_lo,
                           const int* seed_hi, const int* request_key, const int* output_index, int rows, int vocab,
-                          void* scratch, void* stream) {
+                          void* scratch, int* last_token, const int* logit_rows, const int* seq_index,
+                          const int* state_slot, void* stream) {
   if (rows == 0) return 0;
   if (vocab < 1) return fail(2, "sample: vocabulary of %d", vocab);
   if (rows > 65535) return fail(3, "sample: %d rows are more than one launch takes", rows);
   const int chunks = (vocab + CHUNK - 1) / CHUNK;
   if (chunks > 1 && scratch == nullptr) return fail(2, "sample: no scratch for %d chunks", chunks);
+  if (last_token != nullptr && (logit_rows == nullptr || seq_index == nullptr || state_slot == nullptr))
+    return fail(2, "sample: tokens are to be kept for the next step, but the step's rows, entries or slots are missing");
+  const Scatter to{last_token, logit_rows, seq_index, state_slot};
   float* chunk_value = (float*)scratch;
   int* chunk_index = (int*)scratch + (size_t)rows * chunks;
   cudaStream_t s = (cudaStream_t)stream;
   launch_kernel(sample_chunks_kernel, dim3(chunks, rows), THREADS, 0, s, tokens, chunk_value, chunk_index, logits, temperature, seed_lo,
-                                                             seed_hi, request_key, output_index, vocab, chunks);
+                                                             seed_hi, request_key, output_index, vocab, chunks, to);
   if (int err = check_launch("sample")) return err;
   if (chunks > 1) {
-    launch_kernel(sample_rows_kernel, rows, 128, 0, s, tokens, chunk_value, chunk_index, chunks);
+    launch_kernel(sample_rows_kernel, rows, 128, 0, s, tokens, chunk_value, chunk_index, chunks, to);
     return check_launch("sample");
   }
   return 0;

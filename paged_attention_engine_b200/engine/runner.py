@@ -121,8 +121,7 @@ class ModelRunner:
         tokens = None
         if ctx.sampling is not None and logits is not None:
             ops = self.runtime.ops
-            tokens = ops.sample(logits, *ctx.sampling)
-            ops.scatter_tokens(self.last_token, tokens, ctx.logit_rows, ctx.seq_index, ctx.state_slot)
+            tokens = ops.sample(logits, *ctx.sampling, keep=(self.last_token, ctx.logit_rows, ctx.seq_index, ctx.state_slot))
         return logits, tokens
 
     def _graph_key(self, entries, sampling) -> tuple[int, int, int, bool] | None:

@@ -778,8 +778,10 @@ def linear_swiglu(x, weight) -> torch.Tensor:
     return silu_mul(linear(x, weight), SWIGLU_BLOCK)
 
 
-def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> torch.Tensor:
-    """int32 [rows]: argmax where temperature is 0, else the Gumbel-max draw of the row's counters."""
+def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index, keep=None) -> torch.Tensor:
+    """int32 [rows]: argmax where temperature is 0, else the Gumbel-max draw of the row's counters.
+    `keep` = (last_token, logit_rows, seq_index, state_slot): the kernel that picks a row's token
+    also does what `scatter_tokens` would (one launch fewer in a step)."""
     _need(logits, "sample: logits", torch.float32)
     _need(temperature, "sample: temperature", torch.float32)
     for name, t in (("seed_lo", seed_lo), ("seed_hi", seed_hi), ("request_key", request_key), ("output_index", output_index)):
@@ -789,7 +791,15 @@ def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index) -> 
     lib = _lib("sampling")
     words = lib.pae_sample_scratch_words(rows, vocab)
     scratch = torch.empty(words, dtype=torch.int32, device=logits.device) if words else None
+    kept = (None, None, None, None)
+    if keep is not None:
+        kept = keep
+        for name, t in zip(("last_token", "logit_rows", "seq_index", "state_slot"), kept):
+            _need(t, f"sample: {name}", torch.int32)
+        if kept[1].numel() != rows:
+            raise KernelError(f"sample: {rows} rows of logits, {kept[1].numel()} wanted places")
     _check(lib, lib.pae_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(seed_lo), _ptr(seed_hi),
                                _ptr(request_key), _ptr(output_index), rows, vocab, _ptr(scratch),
+                               _ptr(kept[0]), _ptr(kept[1]), _ptr(kept[2]), _ptr(kept[3]),
                                _stream()), 2 if words else 1)
     return out

@@ -165,6 +165,17 @@ def test_sampling(ops, vocab):
     assert got[1].item() == int(torch.argmax(logits[1]))
     logits[5] = logits[2]
     got2 = ops.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), key.cuda(), index.cuda()).cpu()
+    # the same call can also leave every row's token where the next step's embedding looks for it
+    last = torch.full((40,), -7, dtype=torch.int32).cuda()
+    rows_of = torch.tensor([4, 0, 9, 2, 7, 11], dtype=torch.int32).cuda()                # wanted place r is this token row,
+    entry_of = torch.tensor([1, 0, 0, 4, 4, 4, 4, 2, 2, 3, 3, 5], dtype=torch.int32).cuda()   # a token row belongs to this entry,
+    slot_of = torch.tensor([3, 9, 0, 31, 17, 22], dtype=torch.int32).cuda()                # whose state slot this is
+    got3 = ops.sample(logits.cuda(), temperature.cuda(), lo.cuda(), hi.cuda(), key.cuda(), index.cuda(),
+                      keep=(last, rows_of, entry_of, slot_of)).cpu()
+    assert torch.equal(got3, got2)
+    want_last = torch.full((40,), -7, dtype=torch.int32)
+    ref.scatter_tokens(want_last, got2, rows_of.cpu(), entry_of.cpu(), slot_of.cpu())
+    assert torch.equal(last.cpu(), want_last) and int((want_last != -7).sum()) == rows
     assert got2[5] == got2[2], "the same counters and logits draw the same token whatever the row"
     # The device's float32 scores may order two near-equal candidates otherwise than the
     # float64 restatement: the token drawn must score within 1e-4 of the restatement's best.

@@ -135,7 +135,7 @@ def gumbel_scores(row, t, seed_lo, seed_hi, request_key, output_index):
     return row.double().cpu() / t - torch.log(-torch.log(u))
 
 
-def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index):
+def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index, keep=None):
     """Per row: argmax for temperature 0, else Gumbel-max with the engine's counter-based noise."""
     out = torch.empty(logits.shape[0], dtype=torch.int32)
     for r in range(logits.shape[0]):
@@ -144,4 +144,6 @@ def sample(logits, temperature, seed_lo, seed_hi, request_key, output_index):
         if t > 0.0:
             row = gumbel_scores(logits[r], t, seed_lo[r], seed_hi[r], request_key[r], output_index[r])
         out[r] = int(torch.argmax(row))
+    if keep is not None:
+        scatter_tokens(keep[0], out, keep[1], keep[2], keep[3])
     return out
