@@ -314,3 +314,11 @@ def run_trace_program(folder: Path, dtype: str, trace: list[dict], max_tokens: i
         else:
             assert not path.exists()
     return outputs
+
+
+def records_steps() -> bool:
+    """Whether runners record steps as CUDA graphs here: not on the checked build of the kernels
+    (PAE_BOUNDS=1), which hands its limits to the libraries between launches."""
+    from paged_attention_engine_b200.kernels import ops
+
+    return not ops.bounds_checked

