@@ -541,11 +541,12 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
 // 23.4 us with 3 stages of 3 chunks, 24.0 us with 2 of 4, 24.4 us with 4 of 2, 27.0 us with 2 of 2;
 // with one copy per chunk 25.8 us (2 of 4), 33.1 us (8 of 1), 50.2 us (4 of 1). The first in the
 // order of preference whose blocks all run at once is taken (gate|up alone is fastest with 3 stages
-// of 4), unless `pae_linear_few_tokens_configure` has named one for the kind.
+// of 4; with 9 to 16 tokens the activations' chunks take room beside the weights' and 3 stages of 2
+// fit where 3 of 3 do not), unless `pae_linear_few_tokens_configure` has named one for the kind.
 struct Shape {
   int warps, stages, boxes;
 };
-constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 4, 2}, {8, 2, 2}, {8, 3, 3}, {8, 3, 4}};
+constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 4, 2}, {8, 2, 2}, {8, 3, 3}, {8, 3, 4}, {8, 3, 2}};
 constexpr int NUM_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
 int g_forced[3] = {-1, -1, -1};        // index into SHAPES, or -1
 
@@ -556,6 +557,7 @@ size_t shape_bytes(int index, int k) {
     case 1: return shared_bytes<KIND, NT8, 8, SPLIT, 4, 2, NORMED>(k);
     case 2: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(k);
     case 3: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(k);
+    case 5: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(k);
     default: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(k);
   }
 }
@@ -584,7 +586,7 @@ int pick_shape(int k, long blocks, bool* at_once = nullptr) {
   if (at_once != nullptr) *at_once = false;
   int fits = -1;
   // indices into SHAPES in the order of preference
-  static constexpr int NORMED_ORDER[NUM_SHAPES] = {4, 0, 3, 1, 2}, PLAIN_ORDER[NUM_SHAPES] = {3, 0, 1, 2, 4};
+  static constexpr int NORMED_ORDER[NUM_SHAPES] = {4, 0, 3, 1, 5, 2}, PLAIN_ORDER[NUM_SHAPES] = {3, 0, 1, 5, 2, 4};
   for (int at = 0; at < NUM_SHAPES; ++at) {
     const int i = NORMED ? NORMED_ORDER[at] : PLAIN_ORDER[at];
     if (g_forced[KIND] >= 0 && i != g_forced[KIND]) continue;
@@ -607,6 +609,7 @@ int launch_shape(const Params& p, const void* w, int tiles, cudaStream_t stream)
     case 2: return launch_one<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(p, w, tiles, stream);
     case 3: return launch_one<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(p, w, tiles, stream);
     case 4: return launch_one<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(p, w, tiles, stream);
+    case 5: return launch_one<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(p, w, tiles, stream);
   }
   return fail(2, "linear_few_tokens: %d tokens x K = %d do not fit shared memory", p.tokens, p.k);
 }
