@@ -251,3 +251,29 @@ def test_recordings_by_shape_are_few(tmp_path_factory):
     keys = [key[0][0][0] for key in runner.shape_graphs]
     # 5, 6 and 7 are recorded at their second coming, 5 goes when 7 comes; the third 7 is a replay; the third 5 starts over
     assert (keys == [6, 7] and runner.shape_graph_replays == 1) or not helpers.records_steps(), (keys, runner.shape_graph_replays)
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_the_same_prompts_again_through_the_entry_point(tmp_path_factory, dtype_name):
+    """One prompt at a time, four times over, sampled with a temperature: from the second time on
+    the prompt's step has a shape that came before (same length, same state slot) and from the
+    third on it is replayed from its recording, with the sampler's rows and the asynchronous
+    token hand-over inside. Tokens and logits are those of an engine that records nothing."""
+    from paged_attention_engine_b200 import LLM, Request
+
+    folder, raw, page = _folder(tmp_path_factory, "tiny_b", dtype_name)
+    prompts = [tuple(helpers.random_tokens(raw["vocab_size"], n, 500 + 7 * r + n)) for r in range(4) for n in (23, 23, 70)]
+
+    def run(use_graphs):
+        llm = LLM.from_pretrained(folder, dtype=dtype_name, num_blocks=64, block_size=page, record_logits=False,
+                                  use_graphs=use_graphs, max_num_seqs=2)
+        out = {}
+        for i, prompt in enumerate(prompts):
+            llm.add_request(Request(f"q{i}", prompt, 5, temperature=0.8, seed=17))
+            out.update(llm.run_to_completion())
+        return out, llm.runner.shape_graph_replays
+
+    recorded, replays = run(True)
+    eager, none = run(False)
+    assert none == 0 and (replays >= 6 or not helpers.records_steps()), replays
+    assert recorded == eager
