@@ -214,7 +214,15 @@ class ModelRunner:
                 return self._eager(entries, sampling)
             ctx = self.builder.build(entries, sampling)
             slot = _DecodeGraph(ctx.buffer)
-            self._capture(slot, ctx)
+            try:
+                self._capture(slot, ctx)
+            except torch.OutOfMemoryError:
+                # No room for the recording's buffers beside the eager step's: such steps stay eager from here on.
+                self.SHAPE_GRAPHS = 0
+                self.shape_graphs.clear()
+                torch.cuda.empty_cache()
+                logits, tokens = self._run(ctx)
+                return logits, tokens, ctx.num_tokens
             slot.num_tokens = ctx.num_tokens
             self.shape_graphs[key] = slot
             while len(self.shape_graphs) > self.SHAPE_GRAPHS:
