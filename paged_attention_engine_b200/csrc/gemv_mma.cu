@@ -35,7 +35,7 @@
 // activations' chunks [tokens x 64] come through the ring beside the weights' chunks. What the
 // epilogue adds (bias, angles and slots, the residual) is asked for before the main loop.
 //
-// Sizes: K a multiple of 64, at most 16 tokens, head_dim a multiple of 16, and shared memory
+// Sizes: K a multiple of 64, at most 24 tokens, head_dim a multiple of 16, and shared memory
 // for the ring and a normed operand. Everything else is refused here and runs on the tcgen05
 // products and their summing kernels.
 #include "tcgen05.cuh"
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(const __grid_constant_
     }
   }
   // ... and so does the first pass of the norm's weight (NORMED).
-  constexpr int PASS = 8;              // 16-byte units of a token's x per lane and pass
+  constexpr int PASS = TOKENS / WARPS > 2 ? 4 : 8;      // 16-byte units of a token's x per lane and pass
   const int units = p.k >> 3;
   float4 gamma0[PASS][2];
   if (NORMED) {
@@ -618,10 +618,11 @@ template <int KIND, bool SPLIT>
 int launch_tokens(const Params& p, const void* w, int tiles, cudaStream_t stream) {
   const bool normed = p.norm_weight != nullptr;
   if (p.tokens <= 8) return normed ? launch_shape<KIND, 1, SPLIT, true>(p, w, tiles, stream) : launch_shape<KIND, 1, SPLIT, false>(p, w, tiles, stream);
-  return normed ? launch_shape<KIND, 2, SPLIT, true>(p, w, tiles, stream) : launch_shape<KIND, 2, SPLIT, false>(p, w, tiles, stream);
+  if (p.tokens <= 16) return normed ? launch_shape<KIND, 2, SPLIT, true>(p, w, tiles, stream) : launch_shape<KIND, 2, SPLIT, false>(p, w, tiles, stream);
+  return normed ? launch_shape<KIND, 3, SPLIT, true>(p, w, tiles, stream) : launch_shape<KIND, 3, SPLIT, false>(p, w, tiles, stream);
 }
 
-constexpr int MAX_TOKENS = 16;
+constexpr int MAX_TOKENS = 24;
 
 int check_common(const char* what, const void* w, const void* x, const void* norm_weight, const int* error, int tokens, int n, int k) {
   if (tokens < 1 || tokens > MAX_TOKENS) return fail(2, "%s: %d tokens (1 to %d)", what, tokens, MAX_TOKENS);
@@ -639,7 +640,8 @@ int answer(int tokens, long blocks, int k, int normed) {
   bool at_once = false;
   int shape;
   if (tokens <= 8) shape = normed ? pick_shape<KIND, 1, SPLIT, true>(k, blocks, &at_once) : pick_shape<KIND, 1, SPLIT, false>(k, blocks, &at_once);
-  else shape = normed ? pick_shape<KIND, 2, SPLIT, true>(k, blocks, &at_once) : pick_shape<KIND, 2, SPLIT, false>(k, blocks, &at_once);
+  else if (tokens <= 16) shape = normed ? pick_shape<KIND, 2, SPLIT, true>(k, blocks, &at_once) : pick_shape<KIND, 2, SPLIT, false>(k, blocks, &at_once);
+  else shape = normed ? pick_shape<KIND, 3, SPLIT, true>(k, blocks, &at_once) : pick_shape<KIND, 3, SPLIT, false>(k, blocks, &at_once);
   return shape < 0 ? 0 : (at_once ? 2 : 1);
 }
 

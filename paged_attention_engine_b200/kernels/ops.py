@@ -301,8 +301,17 @@ def _rms_norm_now(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Te
 # two); `few_token_products_everywhere` sends every product that the kernels can take at all.
 use_few_token_products = True
 few_token_products_everywhere = False
-FEW_TOKENS_MAX = 16
+FEW_TOKENS_MAX = 24
 QKV_KIND, RESIDUAL_KIND, GATE_UP_KIND = 0, 1, 2
+# Up to how many tokens a kind of product is faster there than as a tcgen05 product with its summing
+# kernel (measured at the 1536-wide sizes, 24 tokens: q|k|v 6.7 against 8.4 us, o 4.9 against 6.5,
+# gate|up 14.3 against 16.5; down, whose warps bring the tokens' operand through their rings once
+# each, 10.2 against 9.6. A decode step of 24 requests: 1.63 against 1.75 ms; with kernels for 32
+# tokens a step of 28 or 32 was no faster, 1.92 against 1.89 and 2.01 against 1.99 ms, and they are not built).
+FEW_TOKENS_MAX_QKV = 24
+FEW_TOKENS_MAX_RESIDUAL = 24          # while K is short ...
+FEW_TOKENS_MAX_RESIDUAL_LONG_K = 16   # ... and from K = 2,048 on
+FEW_TOKENS_MAX_GATE_UP = 24
 
 
 def _few_tokens(x: torch.Tensor, k: int, normed: bool = False, kind: int = GATE_UP_KIND, n: int = 16) -> bool:
@@ -312,7 +321,11 @@ def _few_tokens(x: torch.Tensor, k: int, normed: bool = False, kind: int = GATE_
             and 0 < x.shape[0] <= FEW_TOKENS_MAX and x.data_ptr() % 16 == 0):
         return False
     answer = _lib("gemv_mma").pae_linear_few_tokens_supports(kind, x.shape[0], n, k, 1 if normed else 0)
-    return answer == 2 or (answer == 1 and few_token_products_everywhere)
+    if few_token_products_everywhere:
+        return answer >= 1
+    most = (FEW_TOKENS_MAX_QKV if kind == QKV_KIND else FEW_TOKENS_MAX_GATE_UP if kind == GATE_UP_KIND
+            else FEW_TOKENS_MAX_RESIDUAL if k < SWAPPED_LONG_K else FEW_TOKENS_MAX_RESIDUAL_LONG_K)
+    return answer == 2 and x.shape[0] <= most
 
 
 def _norm_of(x):

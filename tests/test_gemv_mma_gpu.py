@@ -1,4 +1,4 @@
-"""The products of up to 16 tokens as single mma.sync kernels (csrc/gemv_mma.cu) against the plain
+"""The products of up to 24 tokens as single mma.sync kernels (csrc/gemv_mma.cu) against the plain
 reference, each kind alone and at other sizes than the engine's: o and down (+ residual),
 gate|up with SiLU x up, q|k|v with bias, rotation and page write; each with and without the
 RMSNorm of its input folded in; every built launch shape; the same bits whatever the batch; what
@@ -82,7 +82,7 @@ def _norm_weight(k, seed):
     return (1 + 0.2 * torch.randn(k, generator=gen)).cuda()
 
 
-@pytest.mark.parametrize("tokens", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("tokens", [1, 3, 8, 9, 16, 17, 24])
 @pytest.mark.parametrize("n,k", [(1536, 8960), (1536, 1536), (509, 128), (136, 64), (3001, 320), (24, 4096)])
 @pytest.mark.parametrize("normed,residual", [(False, True), (False, False), (True, True)])
 def test_o_and_down(ops, tokens, n, k, normed, residual):
@@ -91,7 +91,7 @@ def test_o_and_down(ops, tokens, n, k, normed, residual):
     r = _rand((tokens, n), 3) if residual else None
     gamma = _norm_weight(k, 4) if normed else None
     if not ops._lib("gemv_mma").pae_linear_few_tokens_supports(RESIDUAL, tokens, n, k, int(normed)):
-        assert normed and tokens > 8 and k == 8960, "only a normed operand of 16 x 8960 is too large for shared memory"
+        assert normed and ((tokens > 8 and k == 8960) or (tokens > 16 and k == 4096)), "only these normed operands are too large for shared memory"
         with pytest.raises(ops.KernelError, match="shared memory"):
             _linear(ops, x, w, r, gamma, 1e-5)
         return
@@ -102,7 +102,7 @@ def test_o_and_down(ops, tokens, n, k, normed, residual):
     _close(got, want, f"[{tokens},{n},{k}]")
 
 
-@pytest.mark.parametrize("tokens", [1, 5, 8, 12, 16])
+@pytest.mark.parametrize("tokens", [1, 5, 8, 12, 16, 21, 24])
 @pytest.mark.parametrize("inter,k", [(8960, 1536), (176, 64), (48, 320), (2000, 256)])
 @pytest.mark.parametrize("normed", [True, False])
 def test_gate_up_with_silu(ops, tokens, inter, k, normed):
@@ -117,7 +117,7 @@ def test_gate_up_with_silu(ops, tokens, inter, k, normed):
     _close(got, want, f"[{tokens},{inter},{k}]", 2.0 ** -6)
 
 
-@pytest.mark.parametrize("tokens", [1, 7, 8, 11, 16])
+@pytest.mark.parametrize("tokens", [1, 7, 8, 11, 16, 19, 24])
 @pytest.mark.parametrize("heads,kv_heads,d,page,k", [(12, 2, 128, 16, 1536), (3, 1, 32, 16, 64), (5, 5, 48, 8, 320), (4, 2, 64, 16, 256),
                                                       (2, 1, 80, 16, 128)])
 @pytest.mark.parametrize("normed", [True, False])
@@ -167,7 +167,7 @@ def test_a_token_without_a_slot_is_not_written_and_parts_may_be_absent(ops):
     assert torch.equal(alone, got)
 
 
-@pytest.mark.parametrize("tokens", [4, 13])
+@pytest.mark.parametrize("tokens", [4, 13, 22])
 def test_every_built_shape_gives_the_same_bits(ops, tokens):
     """Stages and chunks per stage change when a piece of a weight row arrives, not the order of a sum."""
     lib = ops._lib("gemv_mma")
@@ -200,14 +200,14 @@ def test_every_built_shape_gives_the_same_bits(ops, tokens):
 
 
 def test_a_tokens_product_does_not_depend_on_the_batch(ops):
-    """Alone, among 7 others, among 15 others: the same sums in the same order, in every kind."""
-    x = _rand((16, 1536), 50)
+    """Alone, among 7 others, among 23 others: the same sums in the same order, in every kind."""
+    x = _rand((24, 1536), 50)
     gamma = _norm_weight(1536, 51)
     wo = _rand((2048, 1536), 52, 0.05)
     wg = ops.interleave_gate_up(_rand((640, 1536), 53, 0.05), _rand((640, 1536), 54, 0.05))
     whole = (_linear(ops, x, wo), _linear(ops, x, wo, None, gamma, 1e-6), _swiglu(ops, x, wg, gamma, 1e-6),
              _qkv(ops, x, wo, None, gamma, 1e-6, None, None, None, None, 12, 2, 128, 16))
-    for count in (1, 8, 9):
+    for count in (1, 8, 9, 16, 17):
         part_x = x[:count].contiguous()
         part = (_linear(ops, part_x, wo), _linear(ops, part_x, wo, None, gamma, 1e-6), _swiglu(ops, part_x, wg, gamma, 1e-6),
                 _qkv(ops, part_x, wo, None, gamma, 1e-6, None, None, None, None, 12, 2, 128, 16))
@@ -217,8 +217,8 @@ def test_a_tokens_product_does_not_depend_on_the_batch(ops):
 
 def test_what_is_refused(ops):
     x, w = _rand((4, 128), 60), _rand((64, 128), 61)
-    with pytest.raises(ops.KernelError, match="17 tokens"):
-        _linear(ops, _rand((17, 128), 62), w)
+    with pytest.raises(ops.KernelError, match="25 tokens"):
+        _linear(ops, _rand((25, 128), 62), w)
     with pytest.raises(ops.KernelError, match="multiple of 64"):
         _linear(ops, _rand((4, 96), 63), _rand((64, 96), 64))
     with pytest.raises(ops.KernelError, match="16-byte boundary"):
@@ -234,7 +234,7 @@ def test_what_is_refused(ops):
     lib = ops._lib("gemv_mma")
     assert lib.pae_linear_few_tokens_supports(RESIDUAL, 16, 32, 16384, 1) == 0
     assert lib.pae_linear_few_tokens_supports(RESIDUAL, 16, 32, 16384, 0) != 0
-    assert lib.pae_linear_few_tokens_supports(RESIDUAL, 17, 32, 128, 0) == 0
+    assert lib.pae_linear_few_tokens_supports(RESIDUAL, 25, 32, 128, 0) == 0
     ops.check_device_errors()
 
 
