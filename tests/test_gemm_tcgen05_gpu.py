@@ -1,6 +1,6 @@
 """The tcgen05 products against the plain reference: the many-token form and the few-token
 (swapped, split-K) form, at sizes with ragged edges in every dimension. The mma.sync kernels
-that take products of up to 16 tokens where they are faster are switched off in this module
+that take products of up to 24 tokens where they are faster are switched off in this module
 (tests/test_gemv_mma_gpu.py is theirs)."""
 
 import pytest
