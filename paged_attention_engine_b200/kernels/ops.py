@@ -320,6 +320,8 @@ def _few_tokens(x: torch.Tensor, k: int, normed: bool = False, kind: int = GATE_
     if not (use_few_token_products and use_tensor_cores and x.dtype == torch.bfloat16 and x.dim() == 2
             and 0 < x.shape[0] <= FEW_TOKENS_MAX and x.data_ptr() % 16 == 0):
         return False
+    if k < 64 or k % 64:        # not for these kernels: their library is not even built for such a model
+        return False
     answer = _lib("gemv_mma").pae_linear_few_tokens_supports(kind, x.shape[0], n, k, 1 if normed else 0)
     if few_token_products_everywhere:
         return answer >= 1
