@@ -27,8 +27,12 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "-shared",
-    "--split-compile", "0",       # a file's kernels are optimised on all cores (the few-token products: 35 -> 18 s)
 ]
+# PAE_SPLIT_COMPILE=1 lets nvcc optimise a file's kernels on all cores (the few-token products build in
+# 18 s instead of 35). Off by default: the kernels it made were slower on the same GPU in the same
+# call (prefill of 2,048 tokens 6.73 to 6.95 ms against 6.52 to 6.53, a decode step 1.046 against 1.018 ms).
+if os.environ.get("PAE_SPLIT_COMPILE", "0") == "1":
+    NVCC_FLAGS += ["--split-compile", "0"]
 
 # family -> sources (the first is compiled, the others are headers it includes)
 FAMILIES: dict[str, list[str]] = {
