@@ -513,6 +513,8 @@ template <int KIND, int NT8, int WARPS, bool SPLIT, int STAGES, int BOXES, bool 
 int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
   const size_t bytes = shared_bytes<KIND, NT8, WARPS, SPLIT, STAGES, BOXES, NORMED>(p.k);
   if (bytes > (size_t)SMEM_LIMIT) return fail(2, "linear_few_tokens: %d tokens x K = %d need %zu bytes of shared memory", p.tokens, p.k, bytes);
+  // A ring that fits no K at all (the activations' chunks beside the weights' for many tokens) is not compiled.
+  if constexpr (shared_bytes<KIND, NT8, WARPS, SPLIT, STAGES, BOXES, NORMED>(CHUNK) <= (size_t)SMEM_LIMIT) {
   auto kernel = gemv_kernel<KIND, NT8, WARPS, SPLIT, STAGES, BOXES, NORMED>;
   // The attribute belongs to the kernel as loaded on one device.
   static size_t configured[64] = {};
@@ -530,6 +532,9 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
   const int blocks = SPLIT ? tiles : (tiles + WARPS - 1) / WARPS;
   launch_kernel(kernel, dim3(blocks), dim3(WARPS * 32), bytes, stream, map_w, map_x, p);
   return check_launch("linear_few_tokens");
+  } else {
+    return fail(2, "linear_few_tokens: no such kernel");
+  }
 }
 
 // What decides the shape of a launch: warps per block, stages per warp's ring and chunks per
@@ -538,7 +543,7 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
 // much of a warp's share of K the ring holds when the wait for the kernel before ends: what it
 // does not hold costs further trips to memory one after the other. Measured at 8 tokens (q|k|v, o,
 // gate|up and down of a 1536-wide model in a row, 28 times over, one copy per stage and operand):
-// 23.4 us with 3 stages of 3 chunks, 24.0 us with 2 of 4, 24.4 us with 4 of 2, 27.0 us with 2 of 2;
+// 23.4 us with 3 stages of 3 chunks, 24.0 us with 2 of 4, 24.4 us with 4 of 2 (not built: the room of 2 of 4), 27.0 us with 2 of 2;
 // with one copy per chunk 25.8 us (2 of 4), 33.1 us (8 of 1), 50.2 us (4 of 1). The first in the
 // order of preference whose blocks all run at once is taken (gate|up alone is fastest with 3 stages
 // of 4; with 9 to 16 tokens the activations' chunks take room beside the weights' and 3 stages of 2
@@ -546,7 +551,7 @@ int launch_one(const Params& p, const void* w, int tiles, cudaStream_t stream) {
 struct Shape {
   int warps, stages, boxes;
 };
-constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 4, 2}, {8, 2, 2}, {8, 3, 3}, {8, 3, 4}, {8, 3, 2}};
+constexpr Shape SHAPES[] = {{8, 2, 4}, {8, 2, 2}, {8, 3, 3}, {8, 3, 4}, {8, 3, 2}};
 constexpr int NUM_SHAPES = sizeof(SHAPES) / sizeof(SHAPES[0]);
 int g_forced[3] = {-1, -1, -1};        // index into SHAPES, or -1
 
@@ -554,10 +559,9 @@ template <int KIND, int NT8, bool SPLIT, bool NORMED>
 size_t shape_bytes(int index, int k) {
   switch (index) {
     case 0: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 4, NORMED>(k);
-    case 1: return shared_bytes<KIND, NT8, 8, SPLIT, 4, 2, NORMED>(k);
-    case 2: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(k);
-    case 3: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(k);
-    case 5: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(k);
+    case 1: return shared_bytes<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(k);
+    case 2: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(k);
+    case 4: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(k);
     default: return shared_bytes<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(k);
   }
 }
@@ -586,7 +590,7 @@ int pick_shape(int k, long blocks, bool* at_once = nullptr) {
   if (at_once != nullptr) *at_once = false;
   int fits = -1;
   // indices into SHAPES in the order of preference
-  static constexpr int NORMED_ORDER[NUM_SHAPES] = {4, 0, 3, 1, 5, 2}, PLAIN_ORDER[NUM_SHAPES] = {3, 0, 1, 5, 2, 4};
+  static constexpr int NORMED_ORDER[NUM_SHAPES] = {3, 0, 2, 4, 1}, PLAIN_ORDER[NUM_SHAPES] = {2, 0, 4, 1, 3};
   for (int at = 0; at < NUM_SHAPES; ++at) {
     const int i = NORMED ? NORMED_ORDER[at] : PLAIN_ORDER[at];
     if (g_forced[KIND] >= 0 && i != g_forced[KIND]) continue;
@@ -605,11 +609,10 @@ template <int KIND, int NT8, bool SPLIT, bool NORMED>
 int launch_shape(const Params& p, const void* w, int tiles, cudaStream_t stream) {
   switch (pick_shape<KIND, NT8, SPLIT, NORMED>(p.k, SPLIT ? tiles : (tiles + 7) / 8)) {
     case 0: return launch_one<KIND, NT8, 8, SPLIT, 2, 4, NORMED>(p, w, tiles, stream);
-    case 1: return launch_one<KIND, NT8, 8, SPLIT, 4, 2, NORMED>(p, w, tiles, stream);
-    case 2: return launch_one<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(p, w, tiles, stream);
-    case 3: return launch_one<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(p, w, tiles, stream);
-    case 4: return launch_one<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(p, w, tiles, stream);
-    case 5: return launch_one<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(p, w, tiles, stream);
+    case 1: return launch_one<KIND, NT8, 8, SPLIT, 2, 2, NORMED>(p, w, tiles, stream);
+    case 2: return launch_one<KIND, NT8, 8, SPLIT, 3, 3, NORMED>(p, w, tiles, stream);
+    case 3: return launch_one<KIND, NT8, 8, SPLIT, 3, 4, NORMED>(p, w, tiles, stream);
+    case 4: return launch_one<KIND, NT8, 8, SPLIT, 3, 2, NORMED>(p, w, tiles, stream);
   }
   return fail(2, "linear_few_tokens: %d tokens x K = %d do not fit shared memory", p.tokens, p.k);
 }

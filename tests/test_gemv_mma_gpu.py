@@ -13,7 +13,7 @@ import torch_ops as ref
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(8, 2, 4), (8, 4, 2), (8, 2, 2), (8, 3, 3), (8, 3, 4), (8, 3, 2)]
+SHAPES = [(8, 2, 4), (8, 2, 2), (8, 3, 3), (8, 3, 4), (8, 3, 2)]
 QKV, RESIDUAL, GATE_UP = 0, 1, 2
 
 
